@@ -15,6 +15,7 @@ from typing import Any, Callable, Dict, Mapping
 from .lfm2 import ConfigError, Lfm2Config
 from .metanex import MetanexConfig
 from .rofulorn import RofulornConfig
+from .fuzelorn import FuzelornConfig
 
 _ARCHITECTURES: Dict[str, Any] = {}
 _MODEL_TYPES: Dict[str, str] = {}
@@ -62,3 +63,4 @@ def load_config(model_dir: str):
 register_architecture("Lfm2ForCausalLM", Lfm2Config, model_type="lfm2")
 register_architecture("Metanex", MetanexConfig)
 register_architecture("Rofulorn", RofulornConfig)
+register_architecture("Fuzelorn", FuzelornConfig)

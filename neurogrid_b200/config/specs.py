@@ -22,9 +22,11 @@ def _names(**kw) -> Mapping[str, str]:
 
 @dataclass(frozen=True)
 class RMSNormSpec:
-    """y = x * rsqrt(mean(x^2) + eps) * w  (weight multiplies directly, no 1+w)."""
+    """y = x * rsqrt(mean(x^2) + eps) * w  (weight multiplies directly, no 1+w).
+    ``tensor``: the weight's name relative to the norm's ("": it is stored under the norm's own name)."""
     size: int
     eps: float
+    tensor: str = "weight"
     kind: str = "rmsnorm"
 
 
@@ -75,6 +77,15 @@ class NoPositionSpec:
 
 
 @dataclass(frozen=True)
+class DistanceBiasSpec:
+    """No rotation; positions enter the scores only: slope_h * (query position - key position) is taken off head h's
+    score, slope_h = 2^(-``exponent`` * (h + 1) / n_heads)."""
+    n_heads: int
+    exponent: float = 8.0
+    kind: str = "distance_bias"
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     """Grouped-query attention over a paged key/value cache.
 
@@ -119,6 +130,11 @@ class MappedAttentionSpec:
     (1 - diff).  ``bias``: q, k, v and the output projection have biases.
     ``cache_window`` / ``cache_keep_first``: what the layer's pages must keep: its own mask, or the widest mask among
     the layers that read its keys and values.
+    ``norm_scope`` "projection": ONE RMS norm over all of q (before it is split into heads) and one over all of k, the
+    weights as long as the projections, instead of a norm per head.  ``q_temp_coef`` c, ``q_temp_every`` m: q is
+    multiplied by 1 + c ln(floor((p + 1) / m) + 1) at position p (c = 0: not).  ``sink``: a learned number per head
+    whose exponential is one more term of the softmax's denominator; it has no key and no value, is not scaled and
+    gets no bias.  A ``position`` with score slopes takes slope_h (i - j) off the scaled (and capped) score.
     """
     hidden: int
     n_heads: int
@@ -137,9 +153,13 @@ class MappedAttentionSpec:
     bias: bool = False
     cache_window: Optional[int] = None
     cache_keep_first: int = 0
+    norm_scope: str = "head"
+    q_temp_coef: float = 0.0
+    q_temp_every: int = 1
+    sink: bool = False
     names: Mapping[str, str] = field(default_factory=lambda: _names(
         q="q", k="k", v="v", o="o", q_bias="q.b", k_bias="k.b", v_bias="v.b", o_bias="o.b", q_norm="q.norm",
-        k_norm="k.norm", lq1="lq1", lk1="lk1", lq2="lq2", lk2="lk2"))
+        k_norm="k.norm", lq1="lq1", lk1="lk1", lq2="lq2", lk2="lk2", sink="sink"))
     kind: str = "mapped_attention"
 
     def __post_init__(self):
@@ -153,6 +173,8 @@ class MappedAttentionSpec:
             raise ValueError("attention window must be >= 1")
         if self.keep_first < 0 or (self.softcap is not None and not self.softcap > 0):
             raise ValueError("keep_first must be >= 0 and softcap positive")
+        if self.norm_scope not in ("head", "projection") or self.q_temp_every < 1:
+            raise ValueError("norm_scope is 'head' or 'projection', q_temp_every at least 1")
 
 
 @dataclass(frozen=True)
@@ -252,16 +274,34 @@ class LatentAttentionSpec:
 
 @dataclass(frozen=True)
 class MoESpec:
-    """Routed experts: of ``n_experts`` SwiGLU experts of width ``expert_ff`` each token uses the ``top_k``
-    with the largest router logits (float32, with a bias), weighted by the softmax over the chosen logits;
-    a shared expert of width ``shared_ff`` (0: none) runs for every token and is added."""
+    """Routed experts: of ``n_experts`` gated experts of width ``expert_ff`` each token uses ``top_k``; a shared expert
+    of width ``shared_ff`` (0: none) runs for every token and is added.
+
+    ``scoring`` "softmax": the top_k largest router logits (float32, with a bias), weighted by the softmax over the
+    chosen logits.  ``scoring`` "sigmoid": scores s = sigmoid(logits), no bias; experts are chosen by s +
+    ``correction`` (a stored vector, if ``correction``) among the ``keep_groups`` best of ``n_groups`` equal groups of
+    neighbouring experts (a group's score: the sum of its two largest choice scores; the other groups' experts cannot
+    be chosen), and weighted by s over the sum of the chosen s (+ 1e-20).
+    ``activation`` "swiglu": silu(gate) * up.  "clamped_glu": g = min(gate, limit), u = clamp(up, -limit, limit),
+    g sigmoid(``glu_alpha`` g) (u + 1); the shared expert has a ``shared_limit`` of its own.
+    ``shared_gate``: the shared expert's output is multiplied by sigmoid(w . x), one number per token."""
     hidden: int
     n_experts: int
     top_k: int
     expert_ff: int
     shared_ff: int = 0
+    scoring: str = "softmax"
+    correction: bool = False
+    n_groups: int = 1
+    keep_groups: int = 1
+    activation: str = "swiglu"
+    limit: float = 0.0
+    shared_limit: float = 0.0
+    glu_alpha: float = 1.702
+    shared_gate: bool = False
     names: Mapping[str, str] = field(default_factory=lambda: _names(
-        expert="e{}", gate="gate", up="up", down="down", router="router", router_bias="router.b", shared="shared"))
+        expert="e{}", gate="gate", up="up", down="down", router="router", router_bias="router.b", shared="shared",
+        correction="correction", shared_gate="shared.sg"))
     kind: str = "moe"
 
     def __post_init__(self):
@@ -269,6 +309,95 @@ class MoESpec:
             raise ValueError(f"moe: top_k {self.top_k} must be in 1..{self.n_experts}")
         if self.top_k > 32:
             raise ValueError("moe: top_k above 32 is not supported")
+        if self.scoring not in ("softmax", "sigmoid") or self.activation not in ("swiglu", "clamped_glu"):
+            raise ValueError("moe: scoring is softmax or sigmoid, activation swiglu or clamped_glu")
+        if self.n_groups < 1 or self.n_experts % self.n_groups or not (1 <= self.keep_groups <= self.n_groups):
+            raise ValueError(f"moe: {self.n_experts} experts do not form {self.n_groups} equal groups of which {self.keep_groups} are kept")
+        if self.top_k > self.keep_groups * (self.n_experts // self.n_groups):
+            raise ValueError("moe: the kept groups hold fewer experts than top_k")
+        if self.scoring == "softmax" and (self.correction or self.n_groups > 1):
+            raise ValueError("moe: a correction and groups go with sigmoid scoring")
+        if self.activation == "clamped_glu" and not (self.limit > 0 and (self.shared_ff == 0 or self.shared_limit > 0)):
+            raise ValueError("moe: the clamped activation needs positive limits")
+        if self.shared_gate and not (self.shared_ff and self.scoring == "sigmoid" and self.activation == "clamped_glu"):
+            raise ValueError("moe: a gate of the shared expert needs a shared expert, sigmoid scoring and the clamped activation")
+
+
+@dataclass(frozen=True)
+class MLPSpec:
+    """down(act(up x + b_up)) + b_down: an ungated feed-forward; ``activation`` "relu2" is the square of relu.
+    ``bias``: both projections have biases."""
+    hidden: int
+    intermediate: int
+    activation: str = "relu2"
+    bias: bool = True
+    names: Mapping[str, str] = field(default_factory=lambda: _names(up="up", down="down", up_bias="up.b", down_bias="down.b"))
+    kind: str = "mlp"
+
+    def __post_init__(self):
+        if self.activation not in ("relu2",):
+            raise ValueError(f"feed-forward: activation must be relu2, got {self.activation!r}")
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """The gated delta rule: a recurrence per value head with a float32 state S [key_dim, value_dim],
+
+        S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q      (the read-out sees the token's own write)
+
+    q and k (``n_qk_heads`` heads of ``key_dim``; value head h uses head h // (n_heads / n_qk_heads)) and v (``n_heads``
+    heads of ``value_dim``) are projections passed through a causal convolution over time per channel (``taps``
+    taps, the last on the current token, no bias, zeros before the start) and silu; q and k are then unit vectors
+    per head (x / sqrt(sum x^2 + 1e-6)), q times key_dim^(-1/2).  beta = sigmoid(W_b x) and the decay
+    g = exp(-exp(A_log) softplus(W_a x + dt_bias)) are one number per value head.  Each head's o is divided by its root
+    mean square (``eps``), multiplied by a weight of ``value_dim`` (shared by heads) and by silu(W_g x), then
+    projected back.  State per request: S (zero at the start) and the convolution's last taps - 1 inputs."""
+    hidden: int
+    n_heads: int
+    n_qk_heads: int
+    key_dim: int
+    value_dim: int
+    taps: int
+    eps: float
+    names: Mapping[str, str] = field(default_factory=lambda: _names(
+        q="q", k="k", v="v", q_conv="q.conv", k_conv="k.conv", v_conv="v.conv", beta="b", decay="a", a_log="A_log",
+        dt_bias="dt_bias", norm="norm", gate="g", o="o"))
+    kind: str = "gated_delta"
+
+    def __post_init__(self):
+        if self.n_heads < 1 or self.n_qk_heads < 1 or self.n_heads % self.n_qk_heads:
+            raise ValueError(f"gated delta: {self.n_heads} value heads are not a multiple of {self.n_qk_heads} query/key heads")
+        if not (1 <= self.key_dim <= 256) or self.value_dim < 1:
+            raise ValueError(f"gated delta: key_dim in [1, 256] and a positive value_dim, got {self.key_dim}, {self.value_dim}")
+        if not (1 <= self.taps <= 8):
+            raise ValueError(f"gated delta: taps must be in [1, 8], got {self.taps}")
+
+
+@dataclass(frozen=True)
+class SideBySideSpec:
+    """Two mixers that read the same input; the result is half the sum of their outputs, each first divided by its
+    root mean square over the model width (``eps``) and multiplied by a plain weight of its own."""
+    hidden: int
+    left: object
+    right: object
+    eps: float
+    names: Mapping[str, str] = field(default_factory=lambda: _names(left="left", right="right", left_out="left.out",
+                                                                   right_out="right.out"))
+    kind: str = "side_by_side"
+
+
+@dataclass(frozen=True)
+class TokenPairSpec:
+    """An embedding of the pair (previous token, token), added to the token's: row (previous * mul_prev + token * mul_cur)
+    mod buckets of a table [buckets + 1, hidden]; a sequence's first token takes the last row."""
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    table_name: str = "bigram"
+
+    def __post_init__(self):
+        if self.buckets < 1 or self.mul_prev < 0 or self.mul_cur < 0:
+            raise ValueError("token pairs: buckets must be positive and the multipliers not negative")
 
 
 @dataclass(frozen=True)
@@ -348,6 +477,8 @@ class ModelSpec:
     embed_scale: float = 1.0                     # the token embeddings are multiplied by this
     position_table_name: Optional[str] = None    # a table [max_positions, hidden] of learned positions, added to the
                                                  # token embeddings (no LFM2 configuration has one)
+    token_pair: Optional[object] = None          # a TokenPairSpec: an embedding of (previous token, token), added too
+    logit_softcap: Optional[float] = None        # logits <- cap * tanh(logits / cap)
 
     def __post_init__(self):
         n = len(self.layers)

@@ -36,7 +36,7 @@ SOURCES: Dict[str, Sequence[str]] = {
     "gemm_sm100": (),
     "attention_sm100": (),
     "input_conv": (), "retention": (), "latent": (), "latent_mma": (), "moe": (), "token_side": (),
-    "mapped_attention": (), "mapped_attention_mma": (),
+    "mapped_attention": (), "mapped_attention_mma": (), "gated_delta": (),
 }
 
 _lock = threading.RLock()

@@ -348,3 +348,134 @@ NG_EXPORT int ng_swiglu(const void* gu, void* out, int n_rows, int I, int ldo, i
     else NG_LAUNCH((swiglu_kernel<float>), grid, 256, 0, stream, (const float*)gu, (float*)out, I, ldo, gelu);
     return ng_launch_status();
 }
+
+// ---------------------------------------------------------------------------------- token-pair embedding
+// h[row] += table[idx], idx = (previous token * mul_prev + token * mul_cur) mod buckets, and idx = buckets (the
+// table's last row) for a request's first token.  The previous token of an entry's first row is the request's last
+// token of the step before, kept in its state slot (int32 [slots]); `pair_state_kernel` leaves there each entry's
+// last token of this step, after every row has read.
+template <typename T>
+__global__ void pair_embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, const int* __restrict__ state,
+                                  const int* __restrict__ cu_q, const int* __restrict__ ctx_before,
+                                  const int* __restrict__ slots, const int* __restrict__ row_entry, float* __restrict__ h,
+                                  int H, int V, int buckets, long long mul_prev, long long mul_cur, int* __restrict__ status) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int row = blockIdx.x;
+    const int e = row_entry[row];
+    if (e < 0) return;
+    const int tok = tokens[row];
+    if (tok < 0 || tok >= V) return;                       // the embedding kernel has set the status bit
+    int prev = -1;
+    if (row > cu_q[e]) prev = tokens[row - 1];
+    else if (ctx_before[e] > 0) prev = state[slots[e]];
+    if (prev >= V) {
+        if (threadIdx.x == 0) atomicOr(status, NG_STATUS_BAD_TOKEN);
+        prev = -1;
+    }
+    const long long idx = prev < 0 ? (long long)buckets : ((long long)prev * mul_prev + (long long)tok * mul_cur) % buckets;
+    const T* src = table + (size_t)idx * H;
+    float* dst = h + (size_t)row * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) dst[j] += ng_ld(src + j);
+}
+
+__global__ void pair_state_kernel(const int* __restrict__ tokens, int* __restrict__ state, const int* __restrict__ cu_q,
+                                  const int* __restrict__ slots, int n_entries) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n_entries) return;
+    const int q0 = cu_q[e], q1 = cu_q[e + 1];
+    if (q1 > q0) state[slots[e]] = tokens[q1 - 1];
+}
+
+NG_EXPORT int ng_pair_embed(const void* table, int table_bf16, const int* tokens, int* state, const int* cu_q,
+                            const int* ctx_before, const int* slots, const int* row_entry, float* h, int n_rows,
+                            int n_entries, int H, int V, int buckets, long long mul_prev, long long mul_cur, int* status,
+                            cudaStream_t stream) {
+    if (n_rows <= 0 || n_entries <= 0) return NG_OK;
+    if (H <= 0 || V <= 0 || buckets <= 0 || mul_prev < 0 || mul_cur < 0) return NG_BAD_SIZE;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_bf16)
+        NG_LAUNCH((pair_embed_kernel<__nv_bfloat16>), n_rows, threads, 0, stream, (const __nv_bfloat16*)table, tokens, state,
+                  cu_q, ctx_before, slots, row_entry, h, H, V, buckets, mul_prev, mul_cur, status);
+    else
+        NG_LAUNCH((pair_embed_kernel<float>), n_rows, threads, 0, stream, (const float*)table, tokens, state, cu_q,
+                  ctx_before, slots, row_entry, h, H, V, buckets, mul_prev, mul_cur, status);
+    NG_LAUNCH((pair_state_kernel), (n_entries + 127) / 128, 128, 0, stream, tokens, state, cu_q, slots, n_entries);
+    return ng_launch_status();
+}
+
+// ---------------------------------------------------------------------------------- two normed inputs, averaged
+// y[row] = 0.5 * (a / rms(a) * wa + b / rms(b) * wb), rms over the row with eps inside the root, float32.  a and b are
+// [N, H] of type TI or stacks of float32 partial sums; `accumulate`: out[row] += y, else out[row] = y (out float32).
+template <typename TO, typename TA, typename TB>
+__global__ void __launch_bounds__(256)
+pair_norm_mean_kernel(const TA* __restrict__ a, int a_parts, size_t a_stride, const TB* __restrict__ b, int b_parts,
+                      size_t b_stride, const float* __restrict__ wa, const float* __restrict__ wb, float* __restrict__ out,
+                      int H, float eps, int accumulate) {
+    __shared__ float red[32];
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const size_t base = (size_t)blockIdx.x * H;
+    float sa = 0.f, sb = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const float x = ng_ld_sum<TO>(a, base + j, a_parts, a_stride), y = ng_ld_sum<TO>(b, base + j, b_parts, b_stride);
+        sa += x * x;
+        sb += y * y;
+    }
+    sa = ng_block_sum(sa, red);
+    sb = ng_block_sum(sb, red);
+    const float ra = rsqrtf(sa / (float)H + eps), rb = rsqrtf(sb / (float)H + eps);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const float x = ng_ld_sum<TO>(a, base + j, a_parts, a_stride), y = ng_ld_sum<TO>(b, base + j, b_parts, b_stride);
+        const float v = 0.5f * (x * ra * wa[j] + y * rb * wb[j]);
+        out[base + j] = accumulate ? out[base + j] + v : v;
+    }
+}
+
+// a_f32 / b_f32: the input is float32 (a_parts partial sums `a_stride` elements apart), else of the activation type
+NG_EXPORT int ng_pair_norm_mean(const void* a, int a_f32, int a_parts, long long a_stride, const void* b, int b_f32,
+                                int b_parts, long long b_stride, const float* wa, const float* wb, float* out, int n_rows,
+                                int H, float eps, int accumulate, int act_bf16, cudaStream_t stream) {
+    if (n_rows <= 0) return NG_OK;
+    if (H <= 0 || a_parts < 1 || b_parts < 1) return NG_BAD_SIZE;
+    typedef __nv_bfloat16 bf;
+#define PNM(TO, TA, TB)                                                                                               \
+    NG_LAUNCH((pair_norm_mean_kernel<TO, TA, TB>), n_rows, 256, 0, stream, (const TA*)a, a_parts, (size_t)a_stride,    \
+              (const TB*)b, b_parts, (size_t)b_stride, wa, wb, out, H, eps, accumulate)
+    if (act_bf16) {
+        if (a_f32 && b_f32) PNM(bf, float, float);
+        else if (a_f32) PNM(bf, float, bf);
+        else if (b_f32) PNM(bf, bf, float);
+        else PNM(bf, bf, bf);
+    } else {
+        PNM(float, float, float);
+    }
+    return ng_launch_status();
+}
+
+// ---------------------------------------------------------------------------------- small in-place maps
+// kind 0: x <- relu(x)^2 (over [n] elements of the activation type);  kind 1: x <- cap * tanh(x / cap) (float32)
+template <typename T>
+__global__ void unary_kernel(T* __restrict__ x, size_t n, int kind, float param) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = ng_ld(x + i);
+    float y;
+    if (kind == 0) { const float r = fmaxf(v, 0.f); y = r * r; }
+    else y = param * tanhf(v / param);
+    ng_st(x + i, y);
+}
+
+NG_EXPORT int ng_unary(void* x, long long n, int kind, float param, int x_bf16, cudaStream_t stream) {
+    if (n <= 0) return NG_OK;
+    if (kind < 0 || kind > 1 || (kind == 1 && !(param > 0.f))) return NG_BAD_SIZE;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 0x7fffffffLL) return NG_BAD_SIZE;
+    if (x_bf16) NG_LAUNCH((unary_kernel<__nv_bfloat16>), (unsigned)blocks, 256, 0, stream, (__nv_bfloat16*)x, (size_t)n, kind, param);
+    else NG_LAUNCH((unary_kernel<float>), (unsigned)blocks, 256, 0, stream, (float*)x, (size_t)n, kind, param);
+    return ng_launch_status();
+}

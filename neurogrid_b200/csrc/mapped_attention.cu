@@ -7,10 +7,13 @@
 //   a_m    = softmax_j(s_m) v_j  over the visible j: j <= pos and (pos - j < window or j < keep_first);
 //            window 0 = every j <= pos
 //   M == 1: o = a_0                          M == 2: o = a_0 - lambda * a_1
+//   slopes (per head, optional): slope_h * (pos - j) is taken off s(j) after the cap
+//   sinks (per head, optional): the softmax's denominator also holds exp(sink_h), a term without key or value
 //   head_norm: o <- o * rsqrt(mean(o^2) + eps) * post_scale  over the head's dv values
 //
-// Two kernels.  ``qkv_prep``: per-head RMS norm of q and k (one weight vector shared by heads and maps),
-// rotation of the first rot_dims coordinates of every map in pairs (2i, 2i+1), q to its buffer, k and v into
+// Two kernels.  ``qkv_prep``: per-head RMS norm of q and k (one weight vector shared by heads and maps; or, `whole`,
+// one norm over all of a row's q and one over all of its k, with weights of that length), q times a temperature
+// 1 + coef * ln(floor((pos + 1) / every) + 1), rotation of the first rot_dims coordinates of every map in pairs (2i, 2i+1), q to its buffer, k and v into
 // their pages.  ``mapped_attention``: a block per (row, query head, run of keys); a warp takes 32 keys of a
 // 128-key tile with a lane per key for the scores of both maps (the key's row read in 16-byte pieces, q from
 // shared memory), keeps an online softmax per map in float32 and adds the weighted values with a lane per pair
@@ -31,8 +34,10 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
                 const float* __restrict__ kw, const float* __restrict__ inv_freq, int rot_dims,
                 T* __restrict__ k_pages, T* __restrict__ v_pages, const int* __restrict__ table, int table_stride,
                 const int* __restrict__ positions, const int* __restrict__ row_entry, int nQ, int nK, int nV, int d,
-                int dv, int page_size, int num_pages, float eps, int* __restrict__ status) {
+                int dv, int page_size, int num_pages, float eps, int* __restrict__ status, int whole, float temp_coef,
+                int temp_every) {
     extern __shared__ float rot[];                      // cos[rot_dims/2], sin[rot_dims/2]
+    __shared__ float red[32];
     ng_pdl_trigger();
     const int row = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -66,12 +71,26 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
         v_base = (p * nV * page_size + slot) * dv;
     }
     const int half = d / 2;
+    // one norm over all of the row's q and one over all of its k: every block of the row forms both sums itself
+    float r_q = 1.f, r_k = 1.f;
+    if (whole) {
+        float sq = 0.f, sk = 0.f;
+        for (int j = threadIdx.x; j < nQ * d; j += MA_THREADS) { const float t = ng_ld(in + j); sq = fmaf(t, t, sq); }
+        for (int j = threadIdx.x; j < nK * d; j += MA_THREADS) { const float t = ng_ld(in + (size_t)nQ * d + j); sk = fmaf(t, t, sk); }
+        sq = ng_block_sum(sq, red);
+        sk = ng_block_sum(sk, red);
+        r_q = rsqrtf(sq / (float)(nQ * d) + eps);
+        if (nK > 0) r_k = rsqrtf(sk / (float)(nK * d) + eps);
+    }
+    const float temp = temp_coef != 0.f ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every + 1)) : 1.f;
     // few rows: the heads are dealt over gridDim.y blocks of a row; many rows: one block walks all heads of its row
     for (int hh = blockIdx.y * MA_WARPS + warp; hh < nQ + nK; hh += MA_WARPS * gridDim.y) {
         const bool is_q = hh < nQ;
         if (!is_q && !page_ok) continue;
         const T* src = in + (size_t)hh * d;
         const float* w = is_q ? qw : kw;
+        if (w && whole) w += (size_t)(is_q ? hh : hh - nQ) * d;        // a weight per coordinate of the projection
+        const float post = is_q ? temp : 1.f;
         float x1[MA_MAX_PAIRS], x2[MA_MAX_PAIRS];
         float ss = 0.f;
 #pragma unroll
@@ -89,7 +108,7 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
             ss += t * t;
         }
         float r = 1.f;
-        if (w) r = rsqrtf(ng_warp_sum(ss) / (float)d + eps);
+        if (w) r = whole ? (is_q ? r_q : r_k) : rsqrtf(ng_warp_sum(ss) / (float)d + eps);
         T* dst = is_q ? qo + (size_t)hh * d : k_pages + k_base + (size_t)(hh - nQ) * page_size * d;
 #pragma unroll
         for (int u = 0; u < MA_MAX_PAIRS; ++u) {
@@ -97,6 +116,7 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
             if (i < half) {
                 float y1 = x1[u], y2 = x2[u];
                 if (w) { y1 = y1 * r * w[2 * i]; y2 = y2 * r * w[2 * i + 1]; }
+                y1 *= post; y2 *= post;
                 if (i < half_rot) {
                     const float c = rot[i], s = rot[half_rot + i];
                     const float z1 = y1 * c - y2 * s, z2 = y2 * c + y1 * s;
@@ -109,7 +129,7 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
         if ((d & 1) && lane == 0) {
             float t = ng_ld(src + d - 1);
             if (w) t = t * r * w[d - 1];
-            ng_st(dst + d - 1, t);
+            ng_st(dst + d - 1, t * post);
         }
     }
     if (page_ok) {
@@ -124,8 +144,10 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
 NG_EXPORT int ng_qkv_prep(const void* qkv, void* q_out, const float* qw, const float* kw, const float* inv_freq,
                           int rot_dims, void* k_pages, void* v_pages, const int* table, int table_stride,
                           const int* positions, const int* row_entry, int n_rows, int nQ, int nK, int nV, int d, int dv,
-                          int page_size, int num_pages, float eps, int* status, int act_bf16, cudaStream_t stream) {
+                          int page_size, int num_pages, float eps, int* status, int whole, float temp_coef, int temp_every,
+                          int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
+    if (temp_every < 1 || (whole && (!qw || (nK > 0 && !kw)))) return NG_BAD_SIZE;
     if (d <= 0 || d > 64 * MA_MAX_PAIRS || dv <= 0 || nQ <= 0 || nK < 0 || nV < 0 || page_size <= 0 || rot_dims < 0 ||
         rot_dims > d || (rot_dims & 1) || (rot_dims > 0 && !inv_freq))
         return NG_BAD_SIZE;
@@ -135,11 +157,12 @@ NG_EXPORT int ng_qkv_prep(const void* qkv, void* q_out, const float* qw, const f
     if (act_bf16)
         NG_LAUNCH((qkv_prep_kernel<__nv_bfloat16>), grid, MA_THREADS, smem, stream, (const __nv_bfloat16*)qkv,
                   (__nv_bfloat16*)q_out, qw, kw, inv_freq, rot_dims, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, table,
-                  table_stride, positions, row_entry, nQ, nK, nV, d, dv, page_size, num_pages, eps, status);
+                  table_stride, positions, row_entry, nQ, nK, nV, d, dv, page_size, num_pages, eps, status, whole, temp_coef,
+                  temp_every);
     else
         NG_LAUNCH((qkv_prep_kernel<float>), grid, MA_THREADS, smem, stream, (const float*)qkv, (float*)q_out, qw, kw,
                   inv_freq, rot_dims, (float*)k_pages, (float*)v_pages, table, table_stride, positions, row_entry, nQ, nK, nV,
-                  d, dv, page_size, num_pages, eps, status);
+                  d, dv, page_size, num_pages, eps, status, whole, temp_coef, temp_every);
     return ng_launch_status();
 }
 
@@ -149,6 +172,7 @@ struct MaParams {
     const int* positions; const int* row_entry; void* out; int out_ld; float* partial;
     int nH, nG, d, dv, page_size, num_pages, window, keep_first, n_splits;
     float scale, softcap, lambda, post_scale, eps; int head_norm;
+    const float* slopes; const float* sinks;            // per head, or null
 };
 
 // the two bfloat16 values of a 32-bit word as float32: a bfloat16 is the upper half of a float32, so a shift and a
@@ -250,6 +274,7 @@ mapped_attention_kernel(const MaParams p) {
     for (int c = threadIdx.x; c < M * d; c += MA_THREADS) q_s[(c / d) * d4 + (c % d)] = ng_ld(q + c);
     __syncthreads();
     const int g = head / (p.nH / p.nG);
+    const float slope = p.slopes ? p.slopes[head] : 0.f;
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int n_sink = min(p.keep_first, lo);
     const int n_keys = n_sink + (pos - lo + 1);          // logical key t: position t (t < n_sink) or lo + t - n_sink
@@ -287,6 +312,7 @@ mapped_attention_kernel(const MaParams p) {
             if (ok) {
                 s = ma_dot(kp + kbase, q_s + m * d4, d, kvec) * p.scale;
                 if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
+                s -= slope * (float)(pos - kpos);
             }
             const float m_new = fmaxf(m_run[m], ng_warp_max(s));
             const float corr = m_run[m] == -INFINITY ? 0.f : expf(m_run[m] - m_new);
@@ -383,7 +409,7 @@ mapped_attention_kernel(const MaParams p) {
     __syncthreads();
     float lf[M];
 #pragma unroll
-    for (int m = 0; m < M; ++m) lf[m] = fin_l[m];
+    for (int m = 0; m < M; ++m) lf[m] = fin_l[m] + (p.sinks ? expf(p.sinks[head] - mt[m]) : 0.f);
     ma_finish<T, M>(p, o, acc_s, lf, red);
 }
 
@@ -414,7 +440,7 @@ mapped_attention_merge_kernel(const MaParams p) {
             const float f = ps[0] == -INFINITY ? 0.f : expf(ps[0] - mt);
             lt += ps[1] * f;
         }
-        lf[m] = lt;
+        lf[m] = lt + (p.sinks ? expf(p.sinks[head] - mt) : 0.f);
         for (int c = threadIdx.x; c < dv; c += MA_THREADS) {
             float a = 0.f;
             for (int s = 0; s < p.n_splits; ++s) {
@@ -449,8 +475,8 @@ NG_EXPORT int ng_mapped_attention(const void* q, const void* k_pages, const void
                                   int table_stride, const int* positions, const int* row_entry, void* out, int out_ld,
                                   float* partial, int n_rows, int nH, int nG, int n_maps, int d, int dv, int page_size,
                                   int num_pages, int window, int keep_first, int n_splits, float scale, float softcap,
-                                  float lambda, float post_scale, float eps, int head_norm, int act_bf16,
-                                  cudaStream_t stream) {
+                                  float lambda, float post_scale, float eps, int head_norm, const float* slopes,
+                                  const float* sinks, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (d <= 0 || dv <= 0 || dv > 64 * MA_DVU || nH <= 0 || nG <= 0 || nH % nG || page_size <= 0 || n_maps < 1 ||
         n_maps > 2 || n_splits < 1 || n_splits > 65535 || nH > 65535 || (n_splits > 1 && !partial) || out_ld < nH * dv ||
@@ -458,22 +484,22 @@ NG_EXPORT int ng_mapped_attention(const void* q, const void* k_pages, const void
         return NG_BAD_SIZE;
     MaParams p{q, k_pages, v_pages, table, table_stride, positions, row_entry, out, out_ld, n_splits > 1 ? partial : nullptr,
                nH, nG, d, dv, page_size, num_pages, window, keep_first, n_splits, scale, softcap, lambda, post_scale, eps,
-               head_norm};
+               head_norm, slopes, sinks};
     if (act_bf16) return n_maps == 2 ? ma_launch<__nv_bfloat16, 2>(p, n_rows, stream) : ma_launch<__nv_bfloat16, 1>(p, n_rows, stream);
     return n_maps == 2 ? ma_launch<float, 2>(p, n_rows, stream) : ma_launch<float, 1>(p, n_rows, stream);
 }
 
 // The runs' states of every (row, head) merged and the heads finished (maps combined, head norm), for states that another
 // kernel left in `partial` (float32 [n_rows, nH, n_splits, n_maps, dv + 2]: maximum, sum, weighted values).  Rows of no
-// entry get zeros.
+// entry get zeros.  `sinks` (per head, or null) adds exp(sink) to every head's sum.
 NG_EXPORT int ng_mapped_attention_merge(float* partial, const int* row_entry, void* out, int out_ld, int n_rows, int nH,
                                         int n_maps, int dv, int n_splits, float lambda, float post_scale, float eps,
-                                        int head_norm, int act_bf16, cudaStream_t stream) {
+                                        int head_norm, const float* sinks, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (!partial || dv <= 0 || dv > 64 * MA_DVU || nH <= 0 || nH > 65535 || n_maps < 1 || n_maps > 2 || n_splits < 1 || out_ld < nH * dv)
         return NG_BAD_SIZE;
     MaParams p{nullptr, nullptr, nullptr, nullptr, 0, nullptr, row_entry, out, out_ld, partial, nH, 1, 0, dv, 1, 0, 0, 0, n_splits,
-               0.f, 0.f, lambda, post_scale, eps, head_norm};
+               0.f, 0.f, lambda, post_scale, eps, head_norm, nullptr, sinks};
     dim3 grid(n_rows, nH);
     const size_t smem = (size_t)n_maps * dv * sizeof(float);
     if (act_bf16) {

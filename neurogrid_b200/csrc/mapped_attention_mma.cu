@@ -3,7 +3,9 @@
 // Same mathematics: float32 scores, float32 online softmax (as powers of two, on the special-function unit), float32 weights.  The products run on the tensor cores
 // without giving that up: q and k are bfloat16 as the cache holds them, so q.k is a float32 sum of exact products;
 // a float32 weight p enters the weighted sum as three bfloat16 terms hi + mid + lo (what is left is below 2^-24 p),
-// each term's products with the bfloat16 values exact in the float32 accumulators.
+// each term's products with the bfloat16 values exact in the float32 accumulators.  A distance bias per head
+// (slope * (position - key position), taken off the score) and a sink per head (exp(sink) in the softmax's sum, no
+// value) are optional.
 //
 // A block takes consecutive rows of one entry and one query head: 64 rows (one map) or 32 rows (two maps; a warp
 // per map and 16 rows, the maps combined in the epilogue), and walks the keys the block's rows can see, kept first
@@ -30,6 +32,7 @@ struct MmaParams {
     int nH, nG, page_size, num_pages, window, keep_first;
     float scale, softcap, lambda, post_scale, eps; int head_norm;
     float* partial; int n_splits;      // GROUP: runs of keys, their states [row, head, run, map, DV + 2]
+    const float* slopes; const float* sinks;    // per head or null: slope * (pos - key position) off every score; exp(sink) in the sum
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
@@ -139,6 +142,12 @@ mapped_attention_mma_kernel(const MmaParams p) {
     const int w_last = GROUP ? pos_first : min(pos_last, w_first + 15);
     const int w_span = GROUP ? 0 : 15;
     const bool warp_live = wt * 16 < n_rows;
+    // the distance bias of this thread's two rows, in the softmax's powers of two (GROUP: a row is a head)
+    float slope_a = 0.f, slope_b = 0.f;
+    if (p.slopes) {
+        slope_a = p.slopes[GROUP ? head + min(row_a, n_rows - 1) : head] * 1.4426950408889634f;
+        slope_b = p.slopes[GROUP ? head + min(row_b, n_rows - 1) : head] * 1.4426950408889634f;
+    }
     float o[DV / 8][4];
 #pragma unroll
     for (int j = 0; j < DV / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
@@ -226,8 +235,9 @@ mapped_attention_mma_kernel(const MmaParams p) {
         // ---- scale, cap, mask; online softmax in float32, in powers of two (scores times log2 e)
         // a tile that every row of the warp sees whole (the bulk of a long window) needs no mask
         bool interior;
+        const int tile_first = t0 < n_sink ? t0 : lo + (t0 - n_sink);      // an interior tile's keys are tile_first + column
         {
-            const int k_first = t0 < n_sink ? t0 : lo + (t0 - n_sink), k_last = k_first + KT - 1;
+            const int k_first = tile_first, k_last = k_first + KT - 1;
             interior = t0 + KT <= n_keys && (t0 >= n_sink || t0 + KT <= n_sink) && (GROUP || wt * 16 + 15 < n_rows) &&
                        k_last <= w_first && (p.window <= 0 || w_first + w_span - k_first < p.window || k_last < p.keep_first) &&
                        !tile_bad_s[it % 3][0] && !tile_bad_s[it % 3][1];
@@ -240,9 +250,13 @@ mapped_attention_mma_kernel(const MmaParams p) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float v = p.softcap > 0.f ? cap2 * tanh_ex2(s[j][e] * inv_cap) : s[j][e] * sc2;
+                const int pos = (e < 2) ? pos_a : pos_b;
+                if (p.slopes) {
+                    const int kp = interior ? tile_first + j * 8 + 2 * tq + (e & 1) : kpos_t[j * 8 + 2 * tq + (e & 1)];
+                    v -= ((e < 2) ? slope_a : slope_b) * (float)(pos - kp);
+                }
                 if (!interior) {
                     const int kpos = kpos_t[j * 8 + 2 * tq + (e & 1)];
-                    const int pos = (e < 2) ? pos_a : pos_b;
                     const bool row_ok = ((e < 2) ? row_a : row_b) < n_rows;
                     const bool vis = row_ok && kpos >= 0 && kpos <= pos && (p.window <= 0 || pos - kpos < p.window || kpos < p.keep_first);
                     v = vis ? v : -INFINITY;
@@ -318,6 +332,11 @@ mapped_attention_mma_kernel(const MmaParams p) {
         }
         return;
     }
+    if (p.sinks) {                                       // the term without key or value, once per row
+        const float sk = p.sinks[head] * 1.4426950408889634f;
+        if (m_a != -INFINITY) l_a += ex2f(sk - m_a);
+        if (m_b != -INFINITY) l_b += ex2f(sk - m_b);
+    }
     const float ia = l_a > 0.f ? 1.f / l_a : 0.f, ib = l_b > 0.f ? 1.f / l_b : 0.f;
 #pragma unroll
     for (int j = 0; j < DV / 8; ++j) {
@@ -375,14 +394,15 @@ NG_EXPORT int ng_mapped_attention_mma(const void* q, const void* k_pages, const 
                                       int table_stride, const int* cu_q, const int* ctx_before, void* out, int out_ld,
                                       int n_entries, int max_q, int nH, int nG, int n_maps, int d, int dv, int page_size,
                                       int num_pages, int window, int keep_first, float scale, float softcap, float lambda,
-                                      float post_scale, float eps, int head_norm, cudaStream_t stream) {
+                                      float post_scale, float eps, int head_norm, const float* slopes, const float* sinks,
+                                      cudaStream_t stream) {
     if (n_entries <= 0 || max_q <= 0) return NG_OK;
     if (d != D || dv != DV || nH <= 0 || nG <= 0 || nH % nG || page_size <= 0 || n_maps < 1 || n_maps > 2 || out_ld < nH * dv ||
         window < 0 || keep_first < 0 || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
         return NG_BAD_SIZE;
     MmaParams p{(const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before, (bf16*)out,
                 out_ld, nH, nG, page_size, num_pages, window, keep_first, scale, softcap, lambda, post_scale, eps, head_norm,
-                nullptr, 1};
+                nullptr, 1, slopes, sinks};
     return n_maps == 2 ? mma_launch<2, false>(p, n_entries, max_q, stream) : mma_launch<1, false>(p, n_entries, max_q, stream);
 }
 
@@ -394,13 +414,14 @@ NG_EXPORT int ng_mapped_attention_group(const void* q, const void* k_pages, cons
                                         int table_stride, const int* cu_q, const int* ctx_before, float* partial,
                                         int n_entries, int n_splits, int nH, int nG, int n_maps, int d, int dv, int page_size,
                                         int num_pages, int window, int keep_first, float scale, float softcap,
-                                        cudaStream_t stream) {
+                                        const float* slopes, cudaStream_t stream) {
     if (n_entries <= 0) return NG_OK;
     if (d != D || dv != DV || nH <= 0 || nG <= 0 || nH % nG || nH / nG > 16 || page_size <= 0 || n_maps < 1 || n_maps > 2 ||
         window < 0 || keep_first < 0 || n_splits < 1 || n_splits > 65535 || !partial || ((uintptr_t)q & 15) ||
         ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
         return NG_BAD_SIZE;
     MmaParams p{(const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before, nullptr, 0,
-                nH, nG, page_size, num_pages, window, keep_first, scale, softcap, 0.f, 1.f, 0.f, 0, partial, n_splits};
+                nH, nG, page_size, num_pages, window, keep_first, scale, softcap, 0.f, 1.f, 0.f, 0, partial, n_splits, slopes,
+                nullptr};
     return n_maps == 2 ? mma_launch<2, true>(p, n_entries, 1, stream) : mma_launch<1, true>(p, n_entries, 1, stream);
 }

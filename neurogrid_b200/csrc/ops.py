@@ -390,12 +390,15 @@ def attn_decode_bf16(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
 def qkv_prep(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
              inv_freq: Optional[torch.Tensor], k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
              table: torch.Tensor, positions: torch.Tensor, row_entry: torch.Tensor, n_q: int, n_k: int, n_v: int,
-             dim: int, vdim: int, eps: float, status: torch.Tensor) -> None:
+             dim: int, vdim: int, eps: float, status: torch.Tensor, *, whole: bool = False, q_temp_coef: float = 0.0,
+             q_temp_every: int = 1) -> None:
     """qkv[N, (n_q + n_k) * dim + n_v * vdim]: every q and k head (a map of a head counts as one) gets its RMS norm
     over ``dim`` (if its weight is given; float32, shared by all heads) and the rotation of its first
     2 * len(inv_freq) coordinates in pairs (2i, 2i+1) by position * inv_freq[i]; q -> q_out[N, n_q * dim],
     k -> k_pages[P, n_k, page, dim], v -> v_pages[P, n_v, page, vdim].  n_k = n_v = 0 (no pages): a layer that
-    reads another layer's keys and values."""
+    reads another layer's keys and values.  ``whole``: ONE norm over all of a row's q (n_q * dim values) and one over
+    all of its k, the weights then float32 [n_q * dim] and [n_k * dim].  ``q_temp_coef`` c, ``q_temp_every`` m: q is
+    multiplied by 1 + c * ln(floor((position + 1) / m) + 1) after its norm."""
     n = q_out.shape[0]
     if q_out.shape != (n, n_q * dim) or qkv.shape != (n, (n_q + n_k) * dim + n_v * vdim) or qkv.dtype != q_out.dtype:
         raise KernelError("qkv_prep: shapes or dtypes do not fit")
@@ -408,12 +411,14 @@ def qkv_prep(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Te
     _f32(q_weight, "q norm weight"), _f32(k_weight, "k norm weight"), _f32(inv_freq, "inv_freq")
     _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry"), _i32(status, "status")
     rot_dims = 2 * inv_freq.numel() if inv_freq is not None else 0
+    if whole and (q_weight is None or q_weight.numel() != n_q * dim or (n_k and (k_weight is None or k_weight.numel() != n_k * dim))):
+        raise KernelError("qkv_prep: a norm over the whole projection needs weights of the projection's length")
     f = _fn("mapped_attention", "ng_qkv_prep", [_c_void_p] * 5 + [_c_int] + [_c_void_p] * 3 + [_c_int] + [_c_void_p] * 2
-            + [_c_int] * 8 + [_c_float, _c_void_p, _c_int, _c_void_p])
+            + [_c_int] * 8 + [_c_float, _c_void_p, _c_int, _c_float, _c_int, _c_int, _c_void_p])
     _check(f(_ptr(qkv), _ptr(q_out), _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), rot_dims,
              _ptr(k_pages) if n_k else None, _ptr(v_pages) if n_v else None, _ptr(table), table.shape[1], _ptr(positions),
              _ptr(row_entry), n, n_q, n_k, n_v, dim, vdim, page_size, num_pages, float(eps), _ptr(status),
-             _act_flag(q_out, "q_out"), _stream()), "qkv_prep")
+             int(bool(whole)), float(q_temp_coef), int(q_temp_every), _act_flag(q_out, "q_out"), _stream()), "qkv_prep")
 
 
 def mapped_attention_partial_floats(n_rows: int, n_heads: int, n_maps: int, vdim: int, n_splits: int) -> int:
@@ -423,14 +428,17 @@ def mapped_attention_partial_floats(n_rows: int, n_heads: int, n_maps: int, vdim
 def mapped_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
                      positions: torch.Tensor, row_entry: torch.Tensor, out: torch.Tensor, n_heads: int, n_maps: int,
                      window: Optional[int], keep_first: int, scale: float, softcap: float, lam: float, head_norm: bool,
-                     post_scale: float, eps: float, n_splits: int = 1, partial: Optional[torch.Tensor] = None) -> None:
+                     post_scale: float, eps: float, n_splits: int = 1, partial: Optional[torch.Tensor] = None,
+                     slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> None:
     """Attention with float32 scores and weights over keys [P, G * n_maps, page, dim] and values [P, G, page, vdim]:
     per head and map m, a_m = softmax(cap(scale * q_m . k_m)) v over the keys j <= pos with pos - j < window or
     j < keep_first (window None: all), cap(s) = softcap * tanh(s / softcap) (softcap 0: none); the head's output is
     a_0 (one map) or a_0 - lam * a_1 (two), then, with ``head_norm``, over its root mean square (eps) times
     ``post_scale``.  ``out`` [N, n_heads * vdim] may be a block of columns of a wider buffer.  ``n_splits`` > 1 cuts
     every row's keys into runs, a block each, merged through ``partial`` (float32,
-    ``mapped_attention_partial_floats`` values): for steps of few rows."""
+    ``mapped_attention_partial_floats`` values): for steps of few rows.  ``slopes`` (float32 [n_heads]): slope[head] *
+    (position - key position) is taken off every score; ``sinks`` (float32 [n_heads]): every softmax's denominator
+    also holds exp(sink[head]), a term that has no key and no value."""
     n = q.shape[0]
     num_pages, n_k, page_size, dim = k_pages.shape
     n_g, vdim = v_pages.shape[1], v_pages.shape[3]
@@ -443,12 +451,12 @@ def mapped_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     if need and (partial is None or partial.numel() < need):
         raise KernelError(f"mapped_attention: the runs need {need} float32 values")
     f = _fn("mapped_attention", "ng_mapped_attention", [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int, _c_void_p]
-            + [_c_int] * 11 + [_c_float] * 5 + [_c_int, _c_int, _c_void_p])
+            + [_c_int] * 11 + [_c_float] * 5 + [_c_int, _c_void_p, _c_void_p, _c_int, _c_void_p])
     _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(positions), _ptr(row_entry),
              out.data_ptr(), _column_block(out, "attention out"), _ptr(partial) if need else None, n, n_heads, n_g, n_maps,
              dim, vdim, page_size, num_pages, int(window or 0), int(keep_first), int(n_splits), float(scale),
              float(softcap or 0.0), float(lam), float(post_scale), float(eps), int(bool(head_norm)),
-             _act_flag(q, "q"), _stream()), "mapped_attention")
+             _slopes(slopes, n_heads), _slopes(sinks, n_heads), _act_flag(q, "q"), _stream()), "mapped_attention")
 
 
 MAPPED_BACKEND = os.environ.get("NEUROGRID_B200_MAPPED", "mma")     # "mma": tensor-core kernel for long bfloat16 steps; "ffma"
@@ -463,7 +471,8 @@ def mapped_attention_mma_takes(dim: int, vdim: int, dtype) -> bool:
 def mapped_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
                          cu_q: torch.Tensor, ctx_before: torch.Tensor, out: torch.Tensor, n_entries: int, max_q: int,
                          n_heads: int, n_maps: int, window: Optional[int], keep_first: int, scale: float, softcap: float,
-                         lam: float, head_norm: bool, post_scale: float, eps: float) -> None:
+                         lam: float, head_norm: bool, post_scale: float, eps: float,
+                         slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> None:
     """``mapped_attention`` for long bfloat16 steps on the tensor cores: scores are float32 sums of exact bfloat16
     products, the float32 softmax weights enter the weighted sum as three bfloat16 terms each.  Rows are named by
     ``cu_q`` [R+1] and ``ctx_before`` [R]; ``max_q`` bounds the longest entry."""
@@ -476,11 +485,12 @@ def mapped_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
         raise KernelError("mapped_attention_mma: shapes or dtypes do not fit")
     _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before")
     f = _fn("mapped_attention_mma", "ng_mapped_attention_mma", [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 12
-            + [_c_float] * 5 + [_c_int, _c_void_p], {"NG_MA_D": dim, "NG_MA_DV": vdim})
+            + [_c_float] * 5 + [_c_int, _c_void_p, _c_void_p, _c_void_p], {"NG_MA_D": dim, "NG_MA_DV": vdim})
     _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before),
              out.data_ptr(), _column_block(out, "attention out"), n_entries, max_q, n_heads, n_g, n_maps, dim, vdim,
              page_size, num_pages, int(window or 0), int(keep_first), float(scale), float(softcap or 0.0), float(lam),
-             float(post_scale), float(eps), int(bool(head_norm)), _stream()), "mapped_attention_mma")
+             float(post_scale), float(eps), int(bool(head_norm)), _slopes(slopes, n_heads), _slopes(sinks, n_heads), _stream()),
+           "mapped_attention_mma")
 
 
 def mapped_attention_group_takes(dim: int, vdim: int, n_heads: int, n_kv_heads: int, dtype) -> bool:
@@ -492,7 +502,8 @@ def mapped_attention_group(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
                            cu_q: torch.Tensor, ctx_before: torch.Tensor, row_entry: torch.Tensor, out: torch.Tensor,
                            partial: torch.Tensor, n_entries: int, n_heads: int, n_maps: int, window: Optional[int],
                            keep_first: int, scale: float, softcap: float, lam: float, head_norm: bool, post_scale: float,
-                           eps: float, n_splits: int) -> None:
+                           eps: float, n_splits: int, slopes: Optional[torch.Tensor] = None,
+                           sinks: Optional[torch.Tensor] = None) -> None:
     """``mapped_attention`` for a step whose entries bring one token each (bfloat16), on the tensor cores: the query
     heads of a KV group are the rows of a tile, every row's keys are cut into ``n_splits`` runs (a block each), and the
     runs' states pass through ``partial`` (float32, ``mapped_attention_partial_floats`` values, also for one run) to
@@ -510,13 +521,15 @@ def mapped_attention_group(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
     _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(row_entry, "row_entry")
     defines = {"NG_MA_D": dim, "NG_MA_DV": vdim}
     f = _fn("mapped_attention_mma", "ng_mapped_attention_group", [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 11
-            + [_c_float] * 2 + [_c_void_p], defines)
+            + [_c_float] * 2 + [_c_void_p, _c_void_p], defines)
     _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before), _ptr(partial),
              n_entries, int(n_splits), n_heads, n_g, n_maps, dim, vdim, page_size, num_pages, int(window or 0), int(keep_first),
-             float(scale), float(softcap or 0.0), _stream()), "mapped_attention_group")
-    g = _fn("mapped_attention", "ng_mapped_attention_merge", [_c_void_p] * 3 + [_c_int] * 6 + [_c_float] * 3 + [_c_int, _c_int, _c_void_p])
+             float(scale), float(softcap or 0.0), _slopes(slopes, n_heads), _stream()), "mapped_attention_group")
+    g = _fn("mapped_attention", "ng_mapped_attention_merge", [_c_void_p] * 3 + [_c_int] * 6 + [_c_float] * 3
+            + [_c_int, _c_void_p, _c_int, _c_void_p])
     _check(g(_ptr(partial), _ptr(row_entry), out.data_ptr(), _column_block(out, "attention out"), n, n_heads, n_maps, vdim,
-             int(n_splits), float(lam), float(post_scale), float(eps), int(bool(head_norm)), 1, _stream()), "mapped_attention_merge")
+             int(n_splits), float(lam), float(post_scale), float(eps), int(bool(head_norm)), _slopes(sinks, n_heads), 1, _stream()),
+           "mapped_attention_merge")
 
 
 # ----------------------------------------------------------------------------- input convolution
@@ -674,7 +687,137 @@ def head_gate(y: torch.Tensor, gate: torch.Tensor, n_heads: int) -> None:
     _check(f(_ptr(y), _ptr(gate), n, n_heads, y.shape[1] // n_heads, _act_flag(y, "head_gate"), _stream()), "head_gate")
 
 
+# ----------------------------------------------------------------------------- gated delta rule
+def gated_delta(p: torch.Tensor, conv_weight: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                norm_weight: torch.Tensor, conv_state: torch.Tensor, state: torch.Tensor, conv_out: torch.Tensor,
+                o_raw: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, ctx_before: torch.Tensor, slots: torch.Tensor,
+                row_entry: torch.Tensor, n_entries: int, max_q: int, n_heads: int, n_qk_heads: int, key_dim: int,
+                value_dim: int, eps: float) -> None:
+    """p[N, C + nH*dv + 2*nH] = q (nG*dk) | k (nG*dk) | v (nH*dv) | gate (nH*dv) | a (nH) | b (nH), C the first three.
+    The q, k, v channels pass a causal convolution per channel (conv_weight float32 [C, L], tap L-1 on the current
+    token; conv_state [slots, L-1, C] float32 carries a request's last inputs) and silu; q and k become unit vectors
+    per head, q times dk^(-1/2); beta = sigmoid(b), g = exp(-exp(a_log) * softplus(a + dt_bias)); per value head
+    (query/key head h // (nH / nG)):  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q, with
+    state[slots, nH, dk, dv] float32; out[N, nH*dv] = o / rms(o) * norm_weight * silu(gate).  ``conv_out``
+    (float32 [N, C]) and ``o_raw`` (float32 [N, nH*dv]) are scratch.  Everything after the projections is float32."""
+    n = p.shape[0]
+    C = (2 * n_qk_heads * key_dim) + n_heads * value_dim
+    ldp = C + n_heads * value_dim + 2 * n_heads
+    L = conv_weight.shape[1]
+    if p.shape != (n, ldp) or conv_weight.shape != (C, L) or conv_state.shape[1:] != (L - 1, C) \
+            or state.shape[1:] != (n_heads, key_dim, value_dim) or conv_out.shape != (n, C) \
+            or o_raw.shape != (n, n_heads * value_dim) or out.shape != o_raw.shape or out.dtype != p.dtype \
+            or a_log.numel() != n_heads or dt_bias.numel() != n_heads or norm_weight.numel() != value_dim:
+        raise KernelError("gated_delta: shapes do not fit")
+    for t, what in ((conv_weight, "conv weight"), (a_log, "A_log"), (dt_bias, "dt_bias"), (norm_weight, "norm weight"),
+                    (conv_state, "conv state"), (state, "state"), (conv_out, "conv scratch"), (o_raw, "output scratch")):
+        _f32(t, what)
+    _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(slots, "slots"), _i32(row_entry, "row_entry")
+    act = _act_flag(p, "gated_delta input")
+    f = _fn("gated_delta", "ng_gd_conv_silu", [_c_void_p, _c_int] + [_c_void_p] * 6 + [_c_int] * 5 + [_c_void_p])
+    _check(f(_ptr(p), ldp, _ptr(conv_weight), _ptr(conv_state), _ptr(conv_out), _ptr(cu_q), _ptr(ctx_before), _ptr(slots),
+             n_entries, int(max_q), C, L, act, _stream()), "gated_delta (convolution)")
+    f = _fn("gated_delta", "ng_gated_delta", [_c_void_p, _c_void_p] + [_c_int] * 3 + [_c_void_p] * 7 + [_c_int] * 6 + [_c_void_p])
+    _check(f(_ptr(conv_out), _ptr(p), ldp, C + n_heads * value_dim, C + n_heads * value_dim + n_heads, _ptr(a_log),
+             _ptr(dt_bias), _ptr(state), _ptr(o_raw), _ptr(cu_q), _ptr(ctx_before), _ptr(slots), n_entries, n_heads,
+             n_qk_heads, key_dim, value_dim, act, _stream()), "gated_delta")
+    f = _fn("gated_delta", "ng_gd_finish", [_c_void_p, _c_void_p, _c_int, _c_int] + [_c_void_p] * 3 + [_c_int] * 3
+            + [_c_float, _c_int, _c_void_p])
+    _check(f(_ptr(o_raw), _ptr(p), ldp, C, _ptr(norm_weight), _ptr(row_entry), _ptr(out), n, n_heads, value_dim, float(eps),
+             act, _stream()), "gated_delta (head norm)")
+
+
+# ----------------------------------------------------------------------------- small parts of a layer or a model
+def pair_embed(table: torch.Tensor, tokens: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, ctx_before: torch.Tensor,
+               slots: torch.Tensor, row_entry: torch.Tensor, h: torch.Tensor, n_entries: int, vocab: int, buckets: int,
+               mul_prev: int, mul_cur: int, status: torch.Tensor) -> None:
+    """h[N,H] (float32) += table[(previous token * mul_prev + token * mul_cur) mod buckets], row ``buckets`` of the
+    table for a request's first token.  ``state`` int32 [slots] carries each request's last token between steps."""
+    n, H = h.shape
+    if table.shape != (buckets + 1, H) or state.dim() != 1:
+        raise KernelError("pair_embed: shapes do not fit")
+    _f32(h, "residual stream"), _i32(tokens, "tokens"), _i32(state, "previous tokens"), _i32(status, "status")
+    _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(slots, "slots"), _i32(row_entry, "row_entry")
+    f = _fn("elementwise", "ng_pair_embed", [_c_void_p, _c_int] + [_c_void_p] * 7 + [_c_int] * 5 + [_c_ll, _c_ll, _c_void_p, _c_void_p])
+    _check(f(_ptr(table, "pair table"), _act_flag(table, "pair table"), _ptr(tokens), _ptr(state), _ptr(cu_q), _ptr(ctx_before),
+             _ptr(slots), _ptr(row_entry), _ptr(h), n, n_entries, H, int(vocab), int(buckets), int(mul_prev), int(mul_cur),
+             _ptr(status), _stream()), "pair_embed")
+
+
+def _maybe_stack(t: torch.Tensor, n: int, H: int, act_dtype, what: str):
+    """(is float32, parts, stride) of [N,H] in the activation dtype or float32, or a float32 stack [S,N,H]."""
+    if t.dim() == 3:
+        if t.dtype != torch.float32 or tuple(t.shape[1:]) != (n, H):
+            raise KernelError(f"{what}: a stack of partial sums must be float32 [S, {n}, {H}]")
+        return 1, t.shape[0], n * H
+    if tuple(t.shape) != (n, H) or t.dtype not in (act_dtype, torch.float32):
+        raise KernelError(f"{what}: expected [{n}, {H}] of {act_dtype}")
+    return int(t.dtype == torch.float32), 1, 0
+
+
+def pair_norm_mean(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, out: torch.Tensor, eps: float,
+                   act_dtype, accumulate: bool = False) -> None:
+    """out[N,H] float32 (+)= 0.5 * (a / rms(a) * wa + b / rms(b) * wb), rms over a row with eps inside the root.
+    a and b: [N,H] of the activation dtype, or float32 stacks [S,N,H] of partial sums."""
+    n, H = out.shape
+    a32, ap, as_ = _maybe_stack(a, n, H, act_dtype, "pair_norm_mean a")
+    b32, bp, bs_ = _maybe_stack(b, n, H, act_dtype, "pair_norm_mean b")
+    _f32(out, "out"), _f32(wa, "weight"), _f32(wb, "weight")
+    f = _fn("elementwise", "ng_pair_norm_mean", [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_ll]
+            + [_c_void_p] * 3 + [_c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(a), a32, ap, as_, _ptr(b), b32, bp, bs_, _ptr(wa), _ptr(wb), _ptr(out), n, H, float(eps),
+             int(bool(accumulate)), int(act_dtype == torch.bfloat16), _stream()), "pair_norm_mean")
+
+
+def relu_squared_(x: torch.Tensor) -> None:
+    """x <- relu(x)^2 in place."""
+    f = _fn("elementwise", "ng_unary", [_c_void_p, _c_ll, _c_int, _c_float, _c_int, _c_void_p])
+    _check(f(_ptr(x), x.numel(), 0, 0.0, _act_flag(x, "activation"), _stream()), "relu_squared")
+
+
+def softcap_(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place (float32 logits)."""
+    _f32(x, "logits")
+    f = _fn("elementwise", "ng_unary", [_c_void_p, _c_ll, _c_int, _c_float, _c_int, _c_void_p])
+    _check(f(_ptr(x), x.numel(), 1, float(cap), 0, _stream()), "softcap")
+
+
 # ----------------------------------------------------------------------------- routed experts
+def moe_router_sigmoid(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor],
+                       w_shared_gate: Optional[torch.Tensor], weights: torch.Tensor, top_k: int, n_groups: int = 1,
+                       keep_groups: int = 1) -> None:
+    """weights[N, E (+1)] float32: scores s = sigmoid(W_r x); the top_k experts by s + correction among the experts
+    of the keep_groups best of n_groups groups of neighbours (a group's score: its two largest choice scores) get
+    s / (sum of the chosen s + 1e-20), the others zero.  With ``w_shared_gate`` (float32 [H]) the last column
+    receives sigmoid(w . x)."""
+    n, H = x.shape
+    E = w_router.shape[0]
+    ldw = weights.shape[1]
+    if w_router.shape != (E, H) or weights.shape[0] != n or ldw != E + (w_shared_gate is not None) \
+            or (correction is not None and correction.numel() != E) or (w_shared_gate is not None and w_shared_gate.numel() != H):
+        raise KernelError("moe_router_sigmoid: shapes do not fit")
+    _f32(w_router, "router weight"), _f32(correction, "correction"), _f32(w_shared_gate, "shared gate"), _f32(weights, "weights")
+    f = _fn("moe", "ng_moe_router_sigmoid", [_c_void_p] * 5 + [_c_int] * 8 + [_c_void_p])
+    _check(f(_ptr(x), _ptr(w_router), _ptr(correction), _ptr(w_shared_gate), _ptr(weights), n, H, E, ldw, int(top_k),
+             int(n_groups), int(keep_groups), _act_flag(x, "router input"), _stream()), "moe_router_sigmoid")
+
+
+def moe_clamped_glu_scaled(gate_up: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, n_experts: int, expert_ff: int,
+                           limit: float, shared_limit: float, alpha: float, shared_gated: bool) -> None:
+    """out[N, I] = g' sigmoid(alpha g') (u' + 1) * w with g' = min(gate, limit), u' = clamp(up, -limit, limit); columns of
+    expert e use ``limit`` and w = weights[N, e], the shared expert's columns behind them ``shared_limit`` and
+    w = weights[N, E] (``shared_gated``) or 1."""
+    n, I = out.shape
+    if gate_up.shape != (n, 2 * I) or gate_up.dtype != out.dtype or weights.shape[0] != n or I < n_experts * expert_ff:
+        raise KernelError("moe_clamped_glu_scaled: shapes do not fit")
+    _f32(weights, "routing weights")
+    f = _fn("moe", "ng_moe_clamped_glu_scaled", [_c_void_p, _c_void_p, _c_int, _c_void_p] + [_c_int] * 4 + [_c_float] * 3
+            + [_c_int, _c_int, _c_void_p])
+    _check(f(_ptr(gate_up), _ptr(weights), weights.shape[1], _ptr(out), n, I, int(n_experts), int(expert_ff), float(limit),
+             float(shared_limit), float(alpha), int(bool(shared_gated)), _act_flag(out, "moe act"), _stream()),
+           "moe_clamped_glu_scaled")
+
+
 def moe_router(x: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor], weights: torch.Tensor,
                top_k: int) -> None:
     """weights[N, E] float32: softmax over the top_k largest of W_r x + b at the chosen experts, zero elsewhere."""

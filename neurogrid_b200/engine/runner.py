@@ -615,6 +615,8 @@ class ModelRunner:
         for e in self.model.spec.schedule:
             lc = st.layers[e.cache]
             views.append(tuple(view(c, e.writes) for c in lc) if isinstance(lc, tuple) else view(lc, e.writes))
+        own = getattr(self.model, "MODEL_CACHE", None)
+        ctx.model_cache = view(st.layers[own], True) if own in st.layers else None      # what the model itself keeps
         return views
 
     def check_status(self) -> None:

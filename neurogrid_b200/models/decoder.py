@@ -19,6 +19,8 @@ from ..weights.decl import TensorDecl
 
 
 class Decoder:
+    MODEL_CACHE = -1       # the cache id of what the model itself keeps per request (no layer's): the previous token
+
     def __init__(self, spec: ModelSpec, *, dtype: torch.dtype, device):
         if dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"compute dtype must be float32 or bfloat16, got {dtype}")
@@ -34,6 +36,7 @@ class Decoder:
         self.embed_table: Optional[torch.Tensor] = None
         self.head_weight: Optional[torch.Tensor] = None
         self.position_table: Optional[torch.Tensor] = None
+        self.pair_table: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ weights
     def tensors(self) -> Dict[str, TensorDecl]:
@@ -50,6 +53,8 @@ class Decoder:
             out[s.head_name] = TensorDecl((s.vocab_size, s.hidden))
         if s.position_table_name:
             out[s.position_table_name] = TensorDecl((s.max_positions, s.hidden))
+        if s.token_pair is not None:
+            out[s.token_pair.table_name] = TensorDecl((s.token_pair.buckets + 1, s.hidden))
         return out
 
     def bind(self, weights: Dict[str, torch.Tensor]) -> None:
@@ -58,6 +63,7 @@ class Decoder:
         self.embed_table = weights[s.embed_name].to(**kw).contiguous()
         self.head_weight = self.embed_table if s.tie_head else weights[s.head_name].to(**kw).contiguous()
         self.position_table = weights[s.position_table_name].to(**kw).contiguous() if s.position_table_name else None
+        self.pair_table = weights[s.token_pair.table_name].to(**kw).contiguous() if s.token_pair is not None else None
         for layer, block in zip(s.layers, self.blocks):
             pre = layer.prefix
             block.bind({k[len(pre):]: v for k, v in weights.items() if k.startswith(pre)})
@@ -75,6 +81,9 @@ class Decoder:
             if not e.writes and type(need).__name__ != "PagedNeed":
                 raise ValueError(f"schedule entry {e}: only paged keys and values can be read by another layer")
             needs[e.cache] = need
+        if self.spec.token_pair is not None:
+            from ..cache.manager import SlotNeed
+            needs[self.MODEL_CACHE] = SlotNeed((), "int32", -1)      # each request's last token
         return needs
 
     def kernels(self):
@@ -140,6 +149,12 @@ class Decoder:
         ops.embed(self.embed_table, ctx.tokens, h, ctx.status, scale=s.embed_scale)
         if self.position_table is not None:                  # learned absolute positions: h += table[position]
             ops.embed(self.position_table, ctx.positions, h, ctx.status, accumulate=True)
+        if self.pair_table is not None:                      # the pair (previous token, token): h += table[row of the pair]
+            tp = s.token_pair
+            if ctx.model_cache is None:
+                raise RuntimeError("the model keeps each request's previous token: the step must hand it that state")
+            ops.pair_embed(self.pair_table, ctx.tokens, ctx.model_cache.state, ctx.cu_q, ctx.ctx_before, ctx.slots,
+                           ctx.row_entry, h, ctx.n_entries, s.vocab_size, tp.buckets, tp.mul_prev, tp.mul_cur, ctx.status)
         return h
 
     def run_entries(self, ctx: StepContext, caches: List[object], entries, h: torch.Tensor, pending):
@@ -161,6 +176,8 @@ class Decoder:
         self.final_norm.forward(h, pending, x, rows=want_rows)
         logits = ctx.ws.buf("logits", n_want, s.vocab_size, torch.float32)
         ops.linear(x, self.head_weight, None, logits)
+        if s.logit_softcap:
+            ops.softcap_(logits, s.logit_softcap)
         return logits
 
     def graph_pieces(self):

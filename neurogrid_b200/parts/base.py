@@ -142,5 +142,6 @@ class StepContext:
     decode_max_ctx: int = 0         # set (with decode_batch) when launch shapes must not follow the batch
     decode_batch: int = 0
     prefill_ctx: int = 0            # set when a graph serves a class of contexts: the context length its portion kernels plan for
+    model_cache: Optional[object] = None   # the view of what the model itself keeps per request (a SlotView), if anything
     fixed_launches: bool = False    # a CUDA graph of a padded step that may hold portions and single tokens: parts launch
                                     # for both kinds whatever the host lists say (the kernels skip what is not there)

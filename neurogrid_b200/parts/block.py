@@ -12,6 +12,8 @@ class PreNormBlock:
     The residual stream ``h`` is float32.  A block receives the previous block's
     feed-forward output as ``pending`` (not yet added) so that each residual sum rides in the
     norm kernel that follows it; it returns its own feed-forward output the same way.
+    ``spec.ffn`` None: the layer has no feed-forward (and no second norm).  A part's tensor with the relative
+    name "" is stored under the part's own name.
     Reference: gpu/engine/conv_layer.cu:220,328-341 and gpu/engine/layer.cu:1662-1765.
     """
 
@@ -22,26 +24,29 @@ class PreNormBlock:
         if not owns_cache:
             mixer_kw["owns_cache"] = False
         self.mixer = registry.build("mixer", spec.mixer, **mixer_kw)
-        self.ffn = registry.build("ffn", spec.ffn, **kw)
+        self.ffn = registry.build("ffn", spec.ffn, **kw) if spec.ffn is not None else None
         self.mixer_norm = registry.build("norm", spec.mixer_norm, **kw)
-        self.ffn_norm = registry.build("norm", spec.ffn_norm, **kw)
+        self.ffn_norm = registry.build("norm", spec.ffn_norm, **kw) if spec.ffn is not None else None
 
     def parts(self):
         n = self.spec.names
-        return {n["mixer"]: self.mixer, n["ffn"]: self.ffn, n["mixer_norm"]: self.mixer_norm,
-                n["ffn_norm"]: self.ffn_norm}
+        roles = {"mixer": self.mixer, "ffn": self.ffn, "mixer_norm": self.mixer_norm, "ffn_norm": self.ffn_norm}
+        return {n[r]: p for r, p in roles.items() if p is not None}
 
     def tensors(self):
         out = {}
         for sub, part in self.parts().items():
             for name, decl in part.tensors().items():
-                out[f"{sub}.{name}"] = decl
+                out[f"{sub}.{name}" if name else sub] = decl
         return out
 
     def bind(self, t):
         for sub, part in self.parts().items():
             pre = sub + "."
-            part.bind({k[len(pre):]: v for k, v in t.items() if k.startswith(pre)})
+            own = {k[len(pre):]: v for k, v in t.items() if k.startswith(pre)}
+            if sub in t:
+                own[""] = t[sub]
+            part.bind(own)
 
     def cache_need(self):
         return self.mixer.cache_need()
@@ -59,6 +64,8 @@ class PreNormBlock:
         ctx.residual = h if ctx.fuse_residual else None      # parts may add their output into it and return None
         x = self.mixer_norm.forward(h, pending, buf)
         m = self.mixer.forward(x, ctx, cache)
+        if self.ffn is None:
+            return m
         x = self.ffn_norm.forward(h, m, buf)
         return self.ffn.forward(x, ctx)
 

@@ -16,7 +16,7 @@ from .registry import register
 @register("mixer", "mapped_attention")
 class MappedAttention:
     """q, k, v projections (stacked into one product when bound, biases added there) -> per-map RMS norm of q and
-    k -> rotation -> k, v into the layer's pages -> per head and map softmax(cap(scale q.k)) v over the visible
+    k (or one norm over the whole of q and one over the whole of k) -> q times its temperature -> rotation -> k, v into the layer's pages -> per head and map softmax(cap(scale q.k)) v over the visible
     keys -> one map: that; two maps: a_0 - lambda a_1, over its root mean square, times (1 - diff) -> output
     projection.  Keys lie in the pages as G * n_maps heads of key_dim, values as G heads of value_dim.  Scores,
     softmax weights, their sums with the values, norms, angles and lambda are float32 in both compute dtypes.
@@ -38,8 +38,9 @@ class MappedAttention:
     def __init__(self, spec, *, dtype, device, owns_cache=True):
         self.spec, self.dtype, self.device, self.owns_cache = spec, dtype, device, owns_cache
         self.position = registry.build("position", spec.position, device=device)
-        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_norm = self.k_norm = None
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_norm = self.k_norm = self.sinks = None
         self.lam = 0.0
+        self.whole = getattr(spec, "norm_scope", "head") == "projection"      # one norm over all of q, one over all of k
 
     def _proj(self):
         s = self.spec
@@ -56,12 +57,15 @@ class MappedAttention:
                 d[n[p + "_bias"]] = TensorDecl((rows,), "bias")
             d[n["o_bias"]] = TensorDecl((s.hidden,), "bias")
         if s.qk_norm:
-            d[n["q_norm"]] = TensorDecl((s.key_dim,), "norm")
+            rows = self._proj()
+            d[n["q_norm"]] = TensorDecl((rows["q"] if self.whole else s.key_dim,), "norm")
             if self.owns_cache:
-                d[n["k_norm"]] = TensorDecl((s.key_dim,), "norm")
+                d[n["k_norm"]] = TensorDecl((rows["k"] if self.whole else s.key_dim,), "norm")
         if s.n_maps == 2:
             for v in ("lq1", "lk1", "lq2", "lk2"):
                 d[n[v]] = TensorDecl((s.key_dim,), "bias")
+        if getattr(s, "sink", False):
+            d[n["sink"]] = TensorDecl((s.n_heads,), "bias")
         return d
 
     def bind(self, t):
@@ -77,6 +81,8 @@ class MappedAttention:
             self.q_norm = t[n["q_norm"]].to(**f32).contiguous()
             if self.owns_cache:
                 self.k_norm = t[n["k_norm"]].to(**f32).contiguous()
+        if getattr(s, "sink", False):
+            self.sinks = t[n["sink"]].to(**f32).contiguous()
         if s.n_maps == 2:            # one number per layer, formed in float32 as the stored vectors' products
             v = {k: t[n[k]].to(torch.float32) for k in ("lq1", "lk1", "lq2", "lk2")}
             self.lam = float(torch.exp((v["lq1"] * v["lk1"]).sum()) - torch.exp((v["lq2"] * v["lk2"]).sum())) + float(s.diff)
@@ -153,13 +159,16 @@ class MappedAttention:
             raise NotImplementedError("this mixer rotates pairs (2i, 2i+1)")
         ops.qkv_prep(qkv, q, self.q_norm, self.k_norm if n_k else None, pa.inv_freq, cache.k_pages if n_k else None,
                      cache.v_pages if n_v else None, cache.table, ctx.positions, ctx.row_entry, n_q, n_k, n_v,
-                     s.key_dim, s.value_dim, s.eps, ctx.status)
-        self.attend(q, cache, ctx, out)
+                     s.key_dim, s.value_dim, s.eps, ctx.status, whole=self.whole,
+                     q_temp_coef=getattr(s, "q_temp_coef", 0.0), q_temp_every=getattr(s, "q_temp_every", 1))
+        self.attend(q, cache, ctx, out, pa.score_slopes)
 
-    def attend(self, q, cache, ctx, out):
-        """The attention core over the pages: q [N, n_heads * n_maps * key_dim] as the preparation left it."""
+    def attend(self, q, cache, ctx, out, slopes=None):
+        """The attention core over the pages: q [N, n_heads * n_maps * key_dim] as the preparation left it.
+        ``slopes``: the position encoding's score bias per head, if it has one."""
         s = self.spec
         n = q.shape[0]
+        extra = dict(slopes=slopes, sinks=self.sinks)
         if ctx.max_q == 1 and n <= self.GROUP_MAX_ROWS and not ctx.fixed_launches and \
                 ops.mapped_attention_group_takes(s.key_dim, s.value_dim, s.n_heads, s.n_kv_heads, self.dtype):
             n_splits = self._group_splits(n, cache)
@@ -168,12 +177,13 @@ class MappedAttention:
                                   reserve=max(self.GROUP_MAX_RUNS, min(ctx.ws.max_rows, self.GROUP_MAX_ROWS)) * per_run)
             ops.mapped_attention_group(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, ctx.row_entry,
                                        out, partial, ctx.n_entries, s.n_heads, s.n_maps, s.window, s.keep_first,
-                                       s.softmax_scale, s.softcap or 0.0, self.lam, s.n_maps == 2, 1.0 - s.diff, s.eps, n_splits)
+                                       s.softmax_scale, s.softcap or 0.0, self.lam, s.n_maps == 2, 1.0 - s.diff, s.eps, n_splits,
+                                       **extra)
             return
         if n > self.SPLIT_MAX_ROWS and ops.mapped_attention_mma_takes(s.key_dim, s.value_dim, self.dtype):
             ops.mapped_attention_mma(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
                                      ctx.n_entries, ctx.max_q, s.n_heads, s.n_maps, s.window, s.keep_first,
-                                     s.softmax_scale, s.softcap or 0.0, self.lam, s.n_maps == 2, 1.0 - s.diff, s.eps)
+                                     s.softmax_scale, s.softcap or 0.0, self.lam, s.n_maps == 2, 1.0 - s.diff, s.eps, **extra)
             return
         n_splits = self._splits(n, cache)
         partial = None
@@ -184,9 +194,10 @@ class MappedAttention:
                                                                                        n_splits), torch.float32, reserve=bound)
         ops.mapped_attention(q, cache.k_pages, cache.v_pages, cache.table, ctx.positions, ctx.row_entry, out, s.n_heads,
                              s.n_maps, s.window, s.keep_first, s.softmax_scale, s.softcap or 0.0, self.lam,
-                             s.n_maps == 2, 1.0 - s.diff, s.eps, n_splits, partial)
+                             s.n_maps == 2, 1.0 - s.diff, s.eps, n_splits, partial, **extra)
 
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, out_name="mixer_out"):
+        """``out_name``: the workspace buffer of the result (a caller that runs two mixers on one input names two)."""
         a = ctx.ws.buf("mattn_out", x.shape[0], self.inner_width(), self.dtype)
         self.core(x, ctx, cache, a)
-        return ops.linear_to_residual(a, self.w_o, self.b_o, ctx.ws, "mixer_out", residual=ctx.residual)
+        return ops.linear_to_residual(a, self.w_o, self.b_o, ctx.ws, out_name, residual=ctx.residual)

@@ -22,10 +22,10 @@ class RMSNorm:
         self.weight = None
 
     def tensors(self):
-        return {"weight": TensorDecl((self.spec.size,), "norm")}
+        return {getattr(self.spec, "tensor", "weight"): TensorDecl((self.spec.size,), "norm")}
 
     def bind(self, t):
-        self.weight = t["weight"].to(device=self.device, dtype=torch.float32).contiguous()
+        self.weight = t[getattr(self.spec, "tensor", "weight")].to(device=self.device, dtype=torch.float32).contiguous()
 
     def kernels(self):
         return [("elementwise", None)]

@@ -36,6 +36,20 @@ class Rope:
                             rotary_dims=self.spec.rotary_dims)
 
 
+@register("position", "distance_bias")
+class DistanceBias:
+    """No rotation; slope_h * (query position - key position) is taken off head h's scores,
+    slope_h = 2^(-exponent * (h + 1) / n_heads) (formed in float64, rounded once)."""
+
+    def __init__(self, spec, *, device):
+        self.spec = spec
+        h = torch.arange(1, spec.n_heads + 1, dtype=torch.float64)
+        self.slopes = torch.pow(2.0, -float(spec.exponent) * h / spec.n_heads).to(torch.float32).to(device)
+
+    def kernel_args(self):
+        return PositionArgs(score_slopes=self.slopes)
+
+
 @register("position", "none")
 class NoPosition:
     def __init__(self, spec, *, device):

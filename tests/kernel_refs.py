@@ -72,7 +72,7 @@ def add_layernorm(h, delta, weight, out, eps, rows=None, post=None):
 
 
 def qkv_prep(qkv, q_out, q_weight, k_weight, inv_freq, k_pages, v_pages, table, positions, row_entry, n_q, n_k, n_v,
-             dim, vdim, eps, status):
+             dim, vdim, eps, status, *, whole=False, q_temp_coef=0.0, q_temp_every=1):
     n = qkv.shape[0]
     x = qkv.to(D)
     q = x[:, : n_q * dim].reshape(n, n_q, dim)
@@ -80,7 +80,12 @@ def qkv_prep(qkv, q_out, q_weight, k_weight, inv_freq, k_pages, v_pages, table, 
     v = x[:, (n_q + n_k) * dim:].reshape(n, n_v, vdim)
 
     def norm(t, w):
-        return t if w is None else t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * w.to(D)
+        if w is None:
+            return t
+        if whole:                                                 # one norm over all heads of the row
+            flat = t.reshape(n, -1)
+            return (flat * torch.rsqrt((flat * flat).mean(-1, keepdim=True) + eps) * w.to(D)).reshape(t.shape)
+        return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * w.to(D)
 
     def rot(t):
         if inv_freq is None or inv_freq.numel() == 0:
@@ -93,7 +98,11 @@ def qkv_prep(qkv, q_out, q_weight, k_weight, inv_freq, k_pages, v_pages, table, 
         o[..., 0:r:2], o[..., 1:r:2] = a * c - b * s, b * c + a * s
         return o
 
-    q, k = rot(norm(q, q_weight)), rot(norm(k, k_weight))
+    q, k = norm(q, q_weight), norm(k, k_weight)
+    if q_temp_coef:
+        steps = torch.div(positions.long() + 1, int(q_temp_every), rounding_mode="floor") + 1
+        q = q * (1.0 + q_temp_coef * torch.log(steps.to(D)))[:, None, None]
+    q, k = rot(q), rot(k)
     valid = row_entry >= 0
     qo = q.reshape(n, -1).to(q_out.dtype)
     qo[~valid] = 0
@@ -113,7 +122,7 @@ def qkv_prep(qkv, q_out, q_weight, k_weight, inv_freq, k_pages, v_pages, table, 
 
 
 def mapped_attention(q, k_pages, v_pages, table, positions, row_entry, out, n_heads, n_maps, window, keep_first, scale,
-                     softcap, lam, head_norm, post_scale, eps, n_splits=1, partial=None):
+                     softcap, lam, head_norm, post_scale, eps, n_splits=1, partial=None, slopes=None, sinks=None):
     n = q.shape[0]
     P, n_k, ps, dim = k_pages.shape
     n_g, vdim = v_pages.shape[1], v_pages.shape[3]
@@ -138,12 +147,133 @@ def mapped_attention(q, k_pages, v_pages, table, positions, row_entry, out, n_he
                 s = (K[:, g * n_maps + m] @ qr[h, m]) * scale
                 if softcap:
                     s = softcap * torch.tanh(s / softcap)
-                a.append(torch.softmax(s, 0) @ Vv[:, g])
+                if slopes is not None:
+                    s = s - slopes[h].to(D) * (pos - kp).to(D)
+                if sinks is not None:                              # one more term of the denominator, without a value
+                    w = torch.softmax(torch.cat([s, sinks[h].to(D).reshape(1)]), 0)[:-1]
+                else:
+                    w = torch.softmax(s, 0)
+                a.append(w @ Vv[:, g])
             y = a[0] if n_maps == 1 else a[0] - lam * a[1]
             if head_norm:
                 y = y * torch.rsqrt((y * y).mean() + eps) * post_scale
             o[h] = y
         out[r] = o.reshape(-1).to(out.dtype)
+
+
+def gated_delta(p, conv_weight, a_log, dt_bias, norm_weight, conv_state, state, conv_out, o_raw, out, cu_q, ctx_before, slots,
+                row_entry, n_entries, max_q, n_heads, n_qk_heads, key_dim, value_dim, eps):
+    nH, nG, dk, dv = n_heads, n_qk_heads, key_dim, value_dim
+    C = 2 * nG * dk + nH * dv
+    L = conv_weight.shape[1]
+    cu = cu_q.tolist()
+    out[row_entry < 0] = 0
+    for e in range(n_entries):
+        q0, q1 = cu[e], cu[e + 1]
+        if q1 == q0:
+            continue
+        T = q1 - q0
+        ctx, slot = int(ctx_before[e]), int(slots[e])
+        rows = p[q0:q1].to(D)
+        old = conv_state[slot].to(D).clone()
+        for j in range(L - 1):
+            if ctx - (L - 1) + j < 0:
+                old[j] = 0
+        u = torch.cat([old, rows[:, :C]])
+        c = torch.zeros(T, C, dtype=D, device=p.device)
+        for k in range(L):
+            c += conv_weight[:, k].to(D) * u[k:k + T]
+        conv_state[slot] = u[-(L - 1):].to(torch.float32)
+        c = c * torch.sigmoid(c)
+        unit = lambda t: t / torch.sqrt((t * t).sum(-1, keepdim=True) + 1e-6)
+        qh = unit(c[:, :nG * dk].reshape(T, nG, dk)) * dk ** -0.5
+        kh = unit(c[:, nG * dk:2 * nG * dk].reshape(T, nG, dk))
+        vh = c[:, 2 * nG * dk:].reshape(T, nH, dv)
+        gate = rows[:, C:C + nH * dv].reshape(T, nH, dv)
+        a, b = rows[:, C + nH * dv:C + nH * dv + nH], rows[:, C + nH * dv + nH:]
+        beta = torch.sigmoid(b)
+        g = torch.exp(-torch.exp(a_log.to(D)) * torch.nn.functional.softplus(a + dt_bias.to(D)))
+        S = state[slot].to(D).clone() if ctx > 0 else torch.zeros(nH, dk, dv, dtype=D, device=p.device)
+        o = torch.zeros(T, nH, dv, dtype=D, device=p.device)
+        rep = nH // nG
+        for t in range(T):
+            kt, qt = kh[t].repeat_interleave(rep, 0), qh[t].repeat_interleave(rep, 0)
+            S = S * g[t][:, None, None]
+            uu = beta[t][:, None] * (vh[t] - torch.einsum("hkv,hk->hv", S, kt))
+            S = S + kt[:, :, None] * uu[:, None, :]
+            o[t] = torch.einsum("hkv,hk->hv", S, qt)
+        state[slot] = S.to(torch.float32)
+        y = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * norm_weight.to(D) * (gate * torch.sigmoid(gate))
+        out[q0:q1] = y.reshape(T, nH * dv).to(out.dtype)
+
+
+def pair_embed(table, tokens, state, cu_q, ctx_before, slots, row_entry, h, n_entries, vocab, buckets, mul_prev, mul_cur, status):
+    cu = cu_q.tolist()
+    for e in range(n_entries):
+        q0, q1 = cu[e], cu[e + 1]
+        for r in range(q0, q1):
+            if r > q0:
+                prev = int(tokens[r - 1])
+            else:
+                prev = int(state[int(slots[e])]) if int(ctx_before[e]) > 0 else -1
+            idx = buckets if prev < 0 else (prev * mul_prev + int(tokens[r]) * mul_cur) % buckets
+            h[r] += table[idx].to(h.dtype)
+        if q1 > q0:
+            state[int(slots[e])] = tokens[q1 - 1]
+
+
+def pair_norm_mean(a, b, wa, wb, out, eps, act_dtype, accumulate=False):
+    def whole(t):
+        return t.to(D).sum(0).to(act_dtype).to(D) if t.dim() == 3 and t.shape[0] > 1 else t.reshape(out.shape).to(D)
+    x, y = whole(a), whole(b)
+    over = lambda t: t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps)
+    v = 0.5 * (over(x) * wa.to(D) + over(y) * wb.to(D))
+    out.copy_(((out.to(D) + v) if accumulate else v).to(out.dtype))
+
+
+def relu_squared_(x):
+    x.copy_((torch.relu(x.to(D)) ** 2).to(x.dtype))
+
+
+def softcap_(x, cap):
+    x.copy_((cap * torch.tanh(x.to(D) / cap)).to(x.dtype))
+
+
+def moe_router_sigmoid(x, w_router, correction, w_shared_gate, weights, top_k, n_groups=1, keep_groups=1):
+    n, E = x.shape[0], w_router.shape[0]
+    s = torch.sigmoid(x.to(D) @ w_router.to(D).T)
+    choice = s + (correction.to(D) if correction is not None else 0.0)
+    per = E // n_groups
+    weights.zero_()
+    for r in range(n):
+        c = choice[r].clone()
+        if keep_groups < n_groups:
+            gs = []
+            for g in range(n_groups):
+                top2 = sorted(c[g * per:(g + 1) * per].tolist(), reverse=True)[:2]
+                gs.append(sum(top2))
+            order = sorted(range(n_groups), key=lambda g: (-gs[g], g))
+            for g in order[keep_groups:]:
+                c[g * per:(g + 1) * per] = -math.inf
+        chosen = sorted(range(E), key=lambda e: (-float(c[e]), e))[:top_k]
+        total = sum(float(s[r, e]) for e in chosen) + 1e-20
+        for e in chosen:
+            weights[r, e] = float(s[r, e]) / total
+    if w_shared_gate is not None:
+        weights[:, E] = torch.sigmoid(x.to(D) @ w_shared_gate.to(D)).to(weights.dtype)
+
+
+def moe_clamped_glu_scaled(gate_up, weights, out, n_experts, expert_ff, limit, shared_limit, alpha, shared_gated):
+    n, I = out.shape
+    g, u = gate_up[:, :I].to(D), gate_up[:, I:].to(D)
+    routed = n_experts * expert_ff
+    lim = torch.cat([torch.full((routed,), float(limit), dtype=D), torch.full((I - routed,), float(shared_limit), dtype=D)]).to(g.device)
+    g = torch.minimum(g, lim)
+    u = torch.maximum(torch.minimum(u, lim), -lim)
+    w = weights[:, :n_experts].to(D).repeat_interleave(expert_ff, dim=1)
+    tail = weights[:, n_experts:n_experts + 1].to(D) if shared_gated else torch.ones(n, 1, dtype=D, device=g.device)
+    w = torch.cat([w, tail.expand(n, I - routed)], dim=1)
+    out.copy_((g * torch.sigmoid(alpha * g) * (u + 1.0) * w).to(out.dtype))
 
 
 def gemm_f32(a, w, bias, out):
@@ -283,7 +413,8 @@ def sample(logits, temperature, top_p, uniform, out, scratch):
 
 
 _NAMES = ["gather_tokens", "embed", "add_rmsnorm", "residual_add", "swiglu", "gemm_f32", "linear", "shortconv", "rope_cache",
-          "attention_generic", "sample", "add_layernorm", "qkv_prep", "mapped_attention"]
+          "attention_generic", "sample", "add_layernorm", "qkv_prep", "mapped_attention", "gated_delta", "pair_embed",
+          "pair_norm_mean", "relu_squared_", "softcap_", "moe_router_sigmoid", "moe_clamped_glu_scaled"]
 
 
 def install(monkeypatch):
