@@ -57,3 +57,16 @@ def rofulorn_dirs(tmp_path_factory):
     import rofulorn_models
     return {name: rofulorn_models.write_model(cfg, seed, str(tmp_path_factory.mktemp(f"rofulorn_{name}")))
             for name, (cfg, seed) in rofulorn_models.CONFIGS.items()}
+
+
+@pytest.fixture(scope="session")
+def fuzelorn_dirs(tmp_path_factory):
+    """Model folders for the tiny Fuzelorn configurations; "<name>_calm" has routers that hardly look at the token,
+    for comparisons in bfloat16."""
+    import fuzelorn_models
+    out = {}
+    for name, (cfg, seed) in fuzelorn_models.CONFIGS.items():
+        out[name] = fuzelorn_models.write_model(cfg, seed, str(tmp_path_factory.mktemp(f"fuzelorn_{name}")))
+        out[name + "_calm"] = fuzelorn_models.write_model(cfg, seed, str(tmp_path_factory.mktemp(f"fuzelorn_{name}c")),
+                                                          router_gain=0.02)
+    return out
