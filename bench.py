@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine at the LFM2-1.2B shape, random weights, one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl ours|reference]
-                    [--shape 1.2b|700m|350m] [--prompt-len N] [--workload mixed350m|long700m|metanex|rofulorn]
+                    [--shape 1.2b|700m|350m] [--prompt-len N] [--workload mixed350m|long700m|metanex|rofulorn|fuzelorn]
 
 A "step" is one decode step of the batch.  The default run has the layer sizes of the
 LFM2-1.2B configuration, a batch of 8 and requests that hold 2,048-token prompts and grow
@@ -942,6 +942,172 @@ def attention_kernel_times(eng, l2, pk):
     return out
 
 
+# ---------------------------------------------------------------------------------------------- --workload fuzelorn
+def fuzelorn_config(width, layers):
+    """A Fuzelorn configuration with layers of a real model's sizes: in every layer a windowed attention (heads of 128,
+    four query heads to a key/value head, a window of 1,024) beside a gated delta rule (as many value heads of
+    128 x 128, half as many query/key heads, four taps); the first layer's feed-forward dense, the others' routed
+    (16 experts of width/4 in four groups of which two are kept, top 4, a gated shared expert of width/2)."""
+    heads = width // 128
+    left = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+            "mask": {"size": 1024}, "q_temp": {"coef": 0.1, "every": 1024}}
+    right = {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": width // 4, "limit": 7.0}, "shared": {"ff": width // 2, "limit": 7.0}}
+    dense = {"kind": "dense", "ff": 4 * width}
+    return {"architecture": "Fuzelorn", "vocab": 65536, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "embedding": {"scale": 0.5, "bigram": {"buckets": 100003, "mul_prev": 31, "mul_cur": 17}},
+            "layers": [{"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": dense if i == 0 else moe}
+                       for i in range(layers)]}
+
+
+def run_fuzelorn(args):
+    """Prefill and decode throughput of the Fuzelorn design at layer sizes of a real model, beside Metanex (the closest
+    existing model: layers with a float32 recurrent state, windowed attention with float32 weights, routed experts
+    with a shared one) at equal width and depth, and the design's own kernels one by one beside Metanex's like
+    kernels.  One JSON line.  Random weights, synthetic token ids; CUDA events; the L2 is flushed between timed steps."""
+    import torch
+    pk = peaks()
+    l2 = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda:0")
+    clocks = ClockSampler(0)
+    clocks.start()
+    results = []
+    for width, layers in ((1024, 16), (2048, 16)):
+        row = {"width": width, "layers": layers}
+        for arm, cfg in {"fuzelorn": fuzelorn_config(width, layers), "metanex": metanex_config(width, layers)}.items():
+            eng = design_arm(arm, cfg, row, args, l2)
+            if not args.no_kernels:
+                row[arm + "_kernels"] = (fuzelorn_kernel_times if arm == "fuzelorn" else metanex_kernel_times)(eng, l2, pk)
+            del eng
+            torch.cuda.empty_cache()
+        results.append(row)
+    time.sleep(0.06)
+    clocks.stop()
+    print(json.dumps({"workload": "fuzelorn", "what": "Fuzelorn beside Metanex at equal width and depth: prefill of 2,048 "
+                      "tokens, decode at batch 8 and 1 after 2,048 tokens; each design's own kernels alone",
+                      "results": results, "dtype": "bf16", "data": "synthetic token ids, random-init weights", "peaks": pk,
+                      "clocks": clocks.summary(), "impl": "ours"}))
+
+
+def fuzelorn_kernel_times(eng, l2, pk):
+    """The design's own kernels alone, through the parts' own launch plans (CUDA events around the launches, L2 flushed
+    before, median of 7), for a 2,048-token portion and for 8 single tokens after 2,048: microseconds, the bytes each
+    must move with the fraction of the measured copy bandwidth, and for the recurrence and the attention core the
+    multiply-adds they must do as TFLOP/s."""
+    import torch
+    from neurogrid_b200.csrc import ops
+    from neurogrid_b200.parts import PagedView, StepContext
+    from neurogrid_b200.parts.base import Workspace
+    model, dev = eng.model, eng.device
+    D = model.spec.hidden
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(3)
+    rnd = lambda *s: torch.randn(*s, generator=g, device=dev).to(torch.bfloat16)
+
+    def timed(fn):
+        ts = []
+        for _ in range(9):
+            flush_l2(l2)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        return median(ts[2:])
+
+    out = {"unit": "us"}
+    bw = pk["hbm_gbs"] * 1e9
+
+    def mem(name, us, nbytes, flops=0):
+        out[name] = {"us": round(us, 2), "bytes": int(nbytes), "of_copy_bandwidth": round(nbytes / (us * 1e-6) / bw, 3)}
+        if flops:
+            out[name]["flops"] = int(flops)
+            out[name]["tflops"] = round(flops / (us * 1e-6) / 1e12, 2)
+
+    blk = next(b for b in model.blocks if type(b.ffn).__name__ == "MoE")
+    side, f = blk.mixer, blk.ffn
+    left, right = side.left, side.right
+    ls, rs = left.spec, right.spec
+    need = left.cache_need()
+    ps, n_pages = 16, 8 * 4096 // 16
+    kp, vp = rnd(n_pages, need.n_kv_heads, ps, need.head_dim), rnd(n_pages, *need.value_shape()[:1], ps, need.value_shape()[1])
+    for rows, entries in ((PREFILL_TOKENS, 1), (8, 8)):
+        tag = "prefill2048" if entries == 1 else "decode8"
+        q_len = rows // entries
+        before = 0 if entries == 1 else 2048
+        table = torch.arange(entries * 256, dtype=torch.int32, device=dev).view(entries, 256)
+        ctx = StepContext(n_rows=rows, n_entries=entries, max_q=q_len, tokens=i32([0] * rows),
+                          positions=i32([before + t for e in range(entries) for t in range(q_len)]),
+                          row_entry=i32([e for e in range(entries) for _ in range(q_len)]),
+                          cu_q=i32([q_len * e for e in range(entries + 1)]), ctx_before=i32([before] * entries),
+                          slots=i32(list(range(entries))), status=torch.zeros(1, dtype=torch.int32, device=dev),
+                          ws=Workspace(4096, dev), dtype=torch.bfloat16, q_lens=[q_len] * entries,
+                          ctx_lens=[before] * entries, slot_ids=list(range(entries)))
+        # the pair embedding
+        tp = model.spec.token_pair
+        h = torch.randn(rows, D, generator=g, device=dev)
+        tok = torch.randint(0, model.spec.vocab_size, (rows,), generator=g, device=dev).to(torch.int32)
+        prev = torch.zeros(8, dtype=torch.int32, device=dev)
+        us = timed(lambda: ops.pair_embed(model.pair_table, tok, prev, ctx.cu_q, ctx.ctx_before, ctx.slots, ctx.row_entry, h,
+                                          entries, model.spec.vocab_size, tp.buckets, tp.mul_prev, tp.mul_cur, ctx.status))
+        mem(f"{tag}_pair_embed", us, rows * D * (2 + 4 + 4))
+        # left: norms over the projections, temperature, page write; then the attention core
+        d, dv, H = ls.key_dim, ls.value_dim, ls.n_heads
+        vh = need.value_shape()[0]
+        qkv = rnd(rows, left.w_qkv.shape[0])
+        qb = torch.empty(rows, H * d, dtype=torch.bfloat16, device=dev)
+        pa = left.position.kernel_args()
+        view = PagedView(kp, vp, table)
+        o = torch.empty(rows, H * dv, dtype=torch.bfloat16, device=dev)
+        prep = lambda: ops.qkv_prep(qkv, qb, left.q_norm, left.k_norm, None, kp, vp, table, ctx.positions, ctx.row_entry, H,
+                                    need.n_kv_heads, vh, d, dv, ls.eps, ctx.status, whole=True, q_temp_coef=ls.q_temp_coef,
+                                    q_temp_every=ls.q_temp_every)
+        core = lambda: left.attend(qb, view, ctx, o, pa.score_slopes)
+        prep()
+        core()
+        torch.cuda.synchronize()
+        mem(f"{tag}_attention_prep", timed(prep), 2 * qkv.numel() * 2)
+        window = ls.window
+        pairs = sum(min(t + 1, window) for t in range(rows)) if entries == 1 else rows * min(before + 1, window)
+        keys = min(before + q_len, window)
+        kv_bytes = entries * keys * need.elements_per_token() * 2
+        us = timed(core)
+        mem(f"{tag}_attention_core", us, kv_bytes + 2 * rows * H * d * 2, 2 * pairs * H * (d + dv))
+        out[f"{tag}_attention_core"]["of_tensor_peak"] = round(2 * pairs * H * (d + dv) / (us * 1e-6) / 1e12 / pk["bf16_tflops"], 4)
+        # right: convolution + silu, the recurrence, head norm and gate (one call of the part's launcher)
+        nH, nG, dk, dvr = rs.n_heads, rs.n_qk_heads, rs.key_dim, rs.value_dim
+        C = right.channels
+        p = rnd(rows, right.w_in.shape[0])
+        state = torch.zeros(8, nH, dk, dvr, device=dev)
+        cst = torch.zeros(8, right.taps - 1, C, device=dev)
+        conv = torch.empty(rows, C, device=dev)
+        oraw = torch.empty(rows, nH * dvr, device=dev)
+        og = torch.empty(rows, nH * dvr, dtype=torch.bfloat16, device=dev)
+        run = lambda: ops.gated_delta(p, right.w_conv, right.a_log, right.dt_bias, right.norm, cst, state, conv, oraw, og,
+                                      ctx.cu_q, ctx.ctx_before, ctx.slots, ctx.row_entry, entries, q_len, nH, nG, dk, dvr, rs.eps)
+        run()
+        torch.cuda.synchronize()
+        nbytes = p.numel() * 2 + 2 * conv.numel() * 4 + 2 * oraw.numel() * 4 + og.numel() * 2 + 2 * entries * state[0].numel() * 4
+        mem(f"{tag}_gated_delta", timed(run), nbytes, 6 * rows * nH * dk * dvr)
+        # the two mixers' outputs: norms over the width and the mean
+        a, b = rnd(rows, D), rnd(rows, D)
+        y = torch.empty(rows, D, device=dev)
+        us = timed(lambda: ops.pair_norm_mean(a, b, side.w_left, side.w_right, y, side.spec.eps, torch.bfloat16))
+        mem(f"{tag}_pair_norm_mean", us, 2 * rows * D * 2 + rows * D * 4)
+        # router and the clamped activation with the routing weights
+        fs = f.spec
+        xs, wts = rnd(rows, D), torch.empty(rows, fs.n_experts + 1, device=dev)
+        us = timed(lambda: ops.moe_router_sigmoid(xs, f.w_router, f.correction, f.w_shared_gate, wts, fs.top_k, fs.n_groups,
+                                                  fs.keep_groups))
+        mem(f"{tag}_moe_router", us, rows * D * 2 + f.w_router.numel() * 4 + wts.numel() * 4)
+        gu, act = rnd(rows, 2 * f.width), torch.empty(rows, f.width, dtype=torch.bfloat16, device=dev)
+        us = timed(lambda: ops.moe_clamped_glu_scaled(gu, wts, act, fs.n_experts, fs.expert_ff, fs.limit, fs.shared_limit,
+                                                      fs.glu_alpha, True))
+        mem(f"{tag}_moe_clamped_glu", us, 3 * rows * f.width * 2)
+    return out
+
+
 def run_reference(args):
     """The reference's own library through its stock entry points; same metric, same line."""
     shape_name = SHAPE_NAMES[args.shape]
@@ -1004,7 +1170,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=0,
                     help="tokens each request holds before decoding (default 2,048; the context is twice this)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="", choices=["", "mixed350m", "long700m", "metanex", "rofulorn"],
+    ap.add_argument("--workload", default="", choices=["", "mixed350m", "long700m", "metanex", "rofulorn", "fuzelorn"],
                     help="run another workload of the benchmark set through Engine.generate instead; metanex / rofulorn: "
                          "that design beside LFM2 at equal width and depth, prefill and decode, and its kernels alone")
     ap.add_argument("--repeat", type=int, default=2, help="--workload: runs (the first also warms up and captures graphs)")
@@ -1023,6 +1189,9 @@ def main():
         args.warmup = 3
     if args.workload == "metanex":
         run_metanex(args)
+        return 0
+    if args.workload == "fuzelorn":
+        run_fuzelorn(args)
         return 0
     if args.workload == "rofulorn":
         run_rofulorn(args)
