@@ -1084,8 +1084,12 @@ def fuzelorn_kernel_times(eng, l2, pk):
         conv = torch.empty(rows, C, device=dev)
         oraw = torch.empty(rows, nH * dvr, device=dev)
         og = torch.empty(rows, nH * dvr, dtype=torch.bfloat16, device=dev)
+        chunks = None           # as the part chooses: long portions chunk by chunk, single tokens one by one
+        if q_len >= right.CHUNKED_MIN_ROWS and right._chunked():
+            chunks = torch.empty(ops.gated_delta_chunked_scratch(rows, entries, nH, dk, dvr), device=dev)
         run = lambda: ops.gated_delta(p, right.w_conv, right.a_log, right.dt_bias, right.norm, cst, state, conv, oraw, og,
-                                      ctx.cu_q, ctx.ctx_before, ctx.slots, ctx.row_entry, entries, q_len, nH, nG, dk, dvr, rs.eps)
+                                      ctx.cu_q, ctx.ctx_before, ctx.slots, ctx.row_entry, entries, q_len, nH, nG, dk, dvr, rs.eps,
+                                      chunk_scratch=chunks)
         run()
         torch.cuda.synchronize()
         nbytes = p.numel() * 2 + 2 * conv.numel() * 4 + 2 * oraw.numel() * 4 + og.numel() * 2 + 2 * entries * state[0].numel() * 4

@@ -288,3 +288,480 @@ NG_EXPORT int ng_gd_finish(const float* o_raw, const void* p, int ldp, int off_g
                   row_entry, (float*)out, n_rows, nH, dv, eps);
     return ng_launch_status();
 }
+
+// ------------------------------------------------------------------------------------------ portions, chunk by chunk
+// The same recurrence for long portions, regrouped so that most of the work of a portion's chunks runs side by side.
+// With chunks of GC tokens, S the state before a chunk, cl_t = sum_(s<=t) log g_s inside the chunk (so that the decay
+// from token s to token t is exp(cl_t - cl_s), never above one), and k, q the unit vectors:
+//     A[t][s] = beta_t exp(cl_t - cl_s) (k_t . k_s)   for s < t
+//     (I + A) U  = beta V - diag(beta exp(cl)) K S    hence  U = U' - W S,  (I + A) U' = beta V,  (I + A) W = beta exp(cl) K
+//     S'         = exp(cl_last) S + K~^T U,           K~_t = exp(cl_last - cl_t) k_t
+//     o_t        = exp(cl_t) S^T q_t + sum_(s<=t) exp(cl_t - cl_s) (q_t . k_s) u_s
+// `prep` (a block per chunk and head, all chunks side by side) solves the two triangular systems by substitution, a
+// thread per column, and leaves W (transposed), K~ and cl in the scratch and U' where the outputs will be.  `scan` (a
+// block per request, head and 16 value columns) walks the chunks in order: U = U' - W S in place, S' from K~ and U; the
+// state before each chunk goes to the scratch; the next chunk's tiles are copied asynchronously meanwhile.  `out` (a
+// block per chunk, head and slice of value columns) forms o from q, k, cl, U and the chunk's S, in U's place.
+// Float32 FFMA throughout; the results differ from the token-by-token kernel's by rounding only.  Chunk c of entry e
+// uses slot cu_q[e] / GC + e + c of the scratch, as the chunks of different entries then never meet.
+#define GC 32
+#define GC_THREADS 128
+#define GC_DVS 16          // value columns of a scan block
+#define GC_RED 20          // floats between two threads' partial tiles (no bank conflicts for 16-byte accesses)
+
+struct GcParams {
+    const float* conv; const void* p;
+    int ldp, off_a, off_b;
+    const float* a_log; const float* dt_bias;
+    float* state; float* o_raw;
+    float* wt;              // [slots][nH][dk][GC]
+    float* kt;              // [slots][nH][GC][dk]
+    float* cl;              // [slots][nH][GC]
+    float* sb;              // [slots][nH][dk][dv]: the state before each chunk
+    const int* cu_q; const int* ctx_before; const int* slots;
+    int nH, nG, dk, dv, dvs;
+};
+
+// rows of unit vectors into shared memory [GC][dk+1]: all loads first (many in flight), then a warp per row for the
+// norm; rows past n are zero.  Ends with the block in step.
+__device__ __forceinline__ void gc_load_unit(const float* __restrict__ src, size_t ld, int n, int dk, float mul, float* dst) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, ldk = dk + 1;
+#pragma unroll 8
+    for (int idx = threadIdx.x; idx < GC * dk; idx += GC_THREADS) {
+        const int t = idx / dk, i = idx - t * dk;
+        dst[t * ldk + i] = t < n ? src[(size_t)t * ld + i] : 0.f;
+    }
+    __syncthreads();
+    for (int t = warp; t < n; t += GC_THREADS / 32) {
+        float* x = dst + t * ldk;
+        float ss = 0.f;
+        for (int i = lane; i < dk; i += 32) ss = fmaf(x[i], x[i], ss);
+        const float r = rsqrtf(ng_warp_sum(ss) + 1e-6f) * mul;
+        for (int i = lane; i < dk; i += 32) x[i] *= r;
+    }
+    __syncthreads();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(GC_THREADS)
+gd_chunk_prep_kernel(const GcParams P) {
+    extern __shared__ float sm[];
+    const int dk = P.dk, dv = P.dv, nH = P.nH, ldk = dk + 1;
+    float* Ks = sm;                        // [GC][dk+1]
+    float* As = Ks + GC * ldk;             // [GC][GC]
+    float* cl = As + GC * GC;              // [GC]
+    float* bt = cl + GC;                   // [GC]
+    float* Vs = bt + GC;                   // [GC][dv]
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int c = blockIdx.x, head = blockIdx.y, e = blockIdx.z;
+    const int q0 = P.cu_q[e], qlen = P.cu_q[e + 1] - q0;
+    if (c * GC >= qlen) return;
+    const int n = min(GC, qlen - c * GC), row0 = q0 + c * GC;
+    const size_t slot = (size_t)(q0 / GC + e + c) * nH + head;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int C = 2 * P.nG * dk + nH * dv;
+    const size_t off_k = (size_t)P.nG * dk + (size_t)(head / (nH / P.nG)) * dk;
+    const size_t off_v = 2 * (size_t)P.nG * dk + (size_t)head * dv;
+    const float* conv = ng_after_wait(P.conv) + (size_t)row0 * C;
+#pragma unroll 8
+    for (int idx = tid; idx < GC * dv; idx += GC_THREADS) {
+        const int t = idx / dv, v = idx - t * dv;
+        Vs[idx] = t < n ? conv[(size_t)t * C + off_v + v] : 0.f;
+    }
+    gc_load_unit(conv + off_k, C, n, dk, 1.f, Ks);
+    if (warp == 0) {
+        float lg = 0.f, b = 0.f;
+        if (lane < n) {
+            const T* row = reinterpret_cast<const T*>(ng_after_wait(P.p)) + (size_t)(row0 + lane) * P.ldp;
+            const float a = ng_ld(row + P.off_a + head) + P.dt_bias[head], bb = ng_ld(row + P.off_b + head);
+            const float sp = a > 20.f ? a : log1pf(expf(a));
+            b = 1.f / (1.f + expf(-bb));
+            lg = -expf(P.a_log[head]) * sp;
+        }
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float v = __shfl_up_sync(0xffffffffu, lg, o);
+            if (lane >= o) lg += v;
+        }
+        cl[lane] = lg;
+        bt[lane] = b;
+        P.cl[slot * GC + lane] = lg;
+    }
+    __syncthreads();
+    {   // A: a 2 x 4 tile per thread
+        const int i0 = (tid / 8) * 2, j0 = (tid % 8) * 4;
+        float a[2][4] = {};
+        if (j0 <= i0) {
+            for (int d = 0; d < dk; ++d) {
+                const float ka = Ks[i0 * ldk + d], kb = Ks[(i0 + 1) * ldk + d];
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    const float kv = Ks[(j0 + cc) * ldk + d];
+                    a[0][cc] = fmaf(ka, kv, a[0][cc]);
+                    a[1][cc] = fmaf(kb, kv, a[1][cc]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                const int i = i0 + r, j = j0 + cc;
+                As[i * GC + j] = j < i ? a[r][cc] * bt[i] * expf(cl[i] - cl[j]) : 0.f;
+            }
+    }
+    __syncthreads();
+    // K~ for the state's update
+    const float last = cl[GC - 1];
+    float* kt = P.kt + slot * GC * dk;
+    for (int idx = tid; idx < GC * dk; idx += GC_THREADS) {
+        const int t = idx / dk, i = idx - t * dk;
+        kt[idx] = Ks[t * ldk + i] * expf(last - cl[t]);
+    }
+    // the two systems, a column per thread: x_t = rhs_t - sum_(s<t) A[t][s] x_s
+    float* wt = P.wt + slot * dk * GC;
+    for (int col = tid; col < dk + dv; col += GC_THREADS) {
+        const bool isk = col < dk;
+        float x[GC];
+#pragma unroll
+        for (int t = 0; t < GC; ++t) {
+            float acc;
+            if (isk) acc = bt[t] * expf(cl[t]) * Ks[t * ldk + col];
+            else acc = bt[t] * Vs[t * dv + (col - dk)];
+#pragma unroll
+            for (int s4 = 0; s4 < (t & ~3); s4 += 4) {
+                const float4 av = *reinterpret_cast<const float4*>(As + t * GC + s4);
+                acc = fmaf(-av.x, x[s4], acc);
+                acc = fmaf(-av.y, x[s4 + 1], acc);
+                acc = fmaf(-av.z, x[s4 + 2], acc);
+                acc = fmaf(-av.w, x[s4 + 3], acc);
+            }
+#pragma unroll
+            for (int s = (t & ~3); s < t; ++s) acc = fmaf(-As[t * GC + s], x[s], acc);
+            x[t] = acc;
+        }
+        if (isk) {
+#pragma unroll
+            for (int t = 0; t < GC; t += 4)
+                *reinterpret_cast<float4*>(wt + (size_t)col * GC + t) = make_float4(x[t], x[t + 1], x[t + 2], x[t + 3]);
+        } else {
+            float* dst = P.o_raw + (size_t)row0 * nH * dv + (size_t)head * dv + (col - dk);
+#pragma unroll
+            for (int t = 0; t < GC; ++t)
+                if (t < n) dst[(size_t)t * nH * dv] = x[t];
+        }
+    }
+}
+
+__device__ __forceinline__ void gc_copy16(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void gc_copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void gc_copy_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// NT: 4 x 4 tiles of the state's slice [dk][GC_DVS] a thread keeps in registers (ceil(dk / 4 * 4 / GC_THREADS))
+template <int NT>
+__global__ void __launch_bounds__(GC_THREADS)
+gd_chunk_scan_kernel(const GcParams P) {
+    extern __shared__ float4 sm_aligned[];
+    float* sm = reinterpret_cast<float*>(sm_aligned);
+    const int dk = P.dk, dv = P.dv, nH = P.nH;
+    const int per = 2 * GC * dk + GC * GC_DVS;       // a chunk's tiles: W^T [dk][GC], K~ [GC][dk], U' [GC][GC_DVS]
+    float* tiles = sm;                               // two of them
+    float* Ss = tiles + 2 * per;                     // [dk][GC_DVS]
+    float* Us = Ss + dk * GC_DVS;                    // [GC][GC_DVS]
+    float* red = Us + GC * GC_DVS;                   // [4 warps][32 lanes][GC_RED]
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int v0 = blockIdx.x * GC_DVS, head = blockIdx.y, e = blockIdx.z;
+    const int q0 = P.cu_q[e], qlen = P.cu_q[e + 1] - q0;
+    if (qlen <= 0) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nc = (qlen + GC - 1) / GC;
+    const size_t slot0 = (size_t)(q0 / GC + e) * nH + head;
+    float* u_all = ng_after_wait(P.o_raw) + (size_t)q0 * nH * dv + (size_t)head * dv + v0;
+    const float* wt_all = ng_after_wait(P.wt);
+    const float* kt_all = ng_after_wait(P.kt);
+    const float* cl_all = ng_after_wait(P.cl);
+    float* St = P.state + ((size_t)P.slots[e] * nH + head) * dk * dv + v0;
+    const bool carried = P.ctx_before[e] > 0;
+    const int cg4 = (tid & 3) * 4;                   // the thread's four value columns, in both products
+    float s[NT][4][4];
+#pragma unroll
+    for (int m = 0; m < NT; ++m) {
+        const int i0 = ((tid + m * GC_THREADS) >> 2) * 4;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (carried && i0 + r < dk) v = *reinterpret_cast<const float4*>(St + (size_t)(i0 + r) * dv + cg4);
+            s[m][r][0] = v.x, s[m][r][1] = v.y, s[m][r][2] = v.z, s[m][r][3] = v.w;
+            if (i0 + r < dk) *reinterpret_cast<float4*>(Ss + (i0 + r) * GC_DVS + cg4) = v;
+        }
+    }
+    auto fetch = [&](int c) {
+        float* dst = tiles + (c & 1) * per;
+        const size_t slot = slot0 + (size_t)c * nH;
+        const float* w = wt_all + slot * dk * GC;
+        const float* k = kt_all + slot * GC * dk;
+        for (int idx = tid * 4; idx < GC * dk; idx += GC_THREADS * 4) {
+            gc_copy16(dst + idx, w + idx);
+            gc_copy16(dst + GC * dk + idx, k + idx);
+        }
+        const int n = min(GC, qlen - c * GC);
+        float* up = dst + 2 * GC * dk;
+        for (int idx = tid; idx < GC * (GC_DVS / 4); idx += GC_THREADS) {
+            const int t = idx / (GC_DVS / 4), c4 = (idx % (GC_DVS / 4)) * 4;
+            if (t < n) gc_copy16(up + t * GC_DVS + c4, u_all + (size_t)(c * GC + t) * nH * dv + c4);
+            else *reinterpret_cast<float4*>(up + t * GC_DVS + c4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        gc_copy_commit();
+    };
+    fetch(0);
+    const int dkq = dk / 4;                          // a warp's share of the rows of S in U = U' - W S
+    for (int c = 0; c < nc; ++c) {
+        gc_copy_wait();
+        __syncthreads();                             // chunk c's tiles and the state's slice are in shared memory
+        if (c + 1 < nc) fetch(c + 1);
+        const float* Wt = tiles + (c & 1) * per;
+        const float* Kt = Wt + GC * dk;
+        const float* Up = Kt + GC * dk;
+        const size_t slot = slot0 + (size_t)c * nH;
+        const float last = cl_all[slot * GC + GC - 1];      // asked for here, used after the first product
+        float* sb = P.sb + slot * dk * dv + v0;
+#pragma unroll
+        for (int m = 0; m < NT; ++m) {
+            const int i0 = ((tid + m * GC_THREADS) >> 2) * 4;
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                if (i0 + r < dk)
+                    *reinterpret_cast<float4*>(sb + (size_t)(i0 + r) * dv + cg4) = make_float4(s[m][r][0], s[m][r][1], s[m][r][2], s[m][r][3]);
+        }
+        {   // W S: warp w takes rows w*dkq .. of S, lane (t group, column group) a 4 x 4 tile of the product
+            const int t0 = (lane >> 2) * 4;
+            float acc[4][4] = {};
+            const int i1 = (warp + 1) * dkq;
+#pragma unroll 4
+            for (int i = warp * dkq; i < i1; ++i) {
+                const float4 w4 = *reinterpret_cast<const float4*>(Wt + i * GC + t0);
+                const float4 s4 = *reinterpret_cast<const float4*>(Ss + i * GC_DVS + cg4);
+                const float wv[4] = {w4.x, w4.y, w4.z, w4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) acc[r][cc] = fmaf(wv[r], sv[cc], acc[r][cc]);
+            }
+            float* dst = red + (warp * 32 + lane) * GC_RED;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) *reinterpret_cast<float4*>(dst + r * 4) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+        }
+        __syncthreads();
+        {   // U = U' - (the four warps' parts, in ascending order): thread -> token tid / 4, its four columns
+            const int t = tid >> 2;
+            float4 u = *reinterpret_cast<const float4*>(Up + t * GC_DVS + cg4);
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int w = 0; w < GC_THREADS / 32; ++w) {
+                const float4 x = *reinterpret_cast<const float4*>(red + (w * 32 + (t >> 2) * 4 + (tid & 3)) * GC_RED + (t & 3) * 4);
+                a.x += x.x, a.y += x.y, a.z += x.z, a.w += x.w;
+            }
+            u.x -= a.x, u.y -= a.y, u.z -= a.z, u.w -= a.w;
+            *reinterpret_cast<float4*>(Us + t * GC_DVS + cg4) = u;
+            if (c * GC + t < qlen) *reinterpret_cast<float4*>(u_all + (size_t)(c * GC + t) * nH * dv + cg4) = u;
+        }
+        __syncthreads();
+        const float gam = expf(last);
+#pragma unroll
+        for (int m = 0; m < NT; ++m) {
+            const int i0 = ((tid + m * GC_THREADS) >> 2) * 4;
+            if (i0 < dk) {
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) s[m][r][cc] *= gam;
+#pragma unroll 4
+                for (int t = 0; t < GC; ++t) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(Kt + t * dk + i0);
+                    const float4 u4 = *reinterpret_cast<const float4*>(Us + t * GC_DVS + cg4);
+                    const float kv[4] = {k4.x, k4.y, k4.z, k4.w}, uv[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+#pragma unroll
+                        for (int cc = 0; cc < 4; ++cc) s[m][r][cc] = fmaf(kv[r], uv[cc], s[m][r][cc]);
+                }
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    *reinterpret_cast<float4*>(Ss + (i0 + r) * GC_DVS + cg4) = make_float4(s[m][r][0], s[m][r][1], s[m][r][2], s[m][r][3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < NT; ++m) {
+        const int i0 = ((tid + m * GC_THREADS) >> 2) * 4;
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (i0 + r < dk)
+                *reinterpret_cast<float4*>(St + (size_t)(i0 + r) * dv + cg4) = make_float4(s[m][r][0], s[m][r][1], s[m][r][2], s[m][r][3]);
+    }
+}
+
+template <int DVS>
+__global__ void __launch_bounds__(GC_THREADS)
+gd_chunk_out_kernel(const GcParams P) {
+    extern __shared__ float4 sm_aligned[];
+    float* sm = reinterpret_cast<float*>(sm_aligned);
+    const int dk = P.dk, dv = P.dv, nH = P.nH, ldk = dk + 1, ldp = GC + 1;
+    float* Qs = sm;                        // [GC][dk+1]
+    float* Ks = Qs + GC * ldk;             // [GC][dk+1]
+    float* Us = Ks + GC * ldk;             // [GC][DVS]
+    float* Ps = Us + GC * DVS;             // [GC][GC+1]
+    float* cl = Ps + GC * ldp;             // [GC]
+    float* Ss = cl + GC;                   // [dk][DVS]
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int c = blockIdx.x, e = blockIdx.z, slices = dv / DVS;
+    const int head = blockIdx.y / slices, v0 = (blockIdx.y % slices) * DVS;
+    const int q0 = P.cu_q[e], qlen = P.cu_q[e + 1] - q0;
+    if (c * GC >= qlen) return;
+    const int n = min(GC, qlen - c * GC), row0 = q0 + c * GC;
+    const size_t slot = (size_t)(q0 / GC + e + c) * nH + head;
+    const int tid = threadIdx.x;
+    const int C = 2 * P.nG * dk + nH * dv;
+    const size_t off_q = (size_t)(head / (nH / P.nG)) * dk, off_k = (size_t)P.nG * dk + off_q;
+    const float* conv = ng_after_wait(P.conv) + (size_t)row0 * C;
+    gc_load_unit(conv + off_q, C, n, dk, rsqrtf((float)dk), Qs);
+    gc_load_unit(conv + off_k, C, n, dk, 1.f, Ks);
+    if (tid < GC) cl[tid] = ng_after_wait(P.cl)[slot * GC + tid];
+    float* o = ng_after_wait(P.o_raw) + (size_t)row0 * nH * dv + (size_t)head * dv + v0;
+    for (int idx = tid; idx < GC * (DVS / 4); idx += GC_THREADS) {
+        const int t = idx / (DVS / 4), c4 = (idx % (DVS / 4)) * 4;
+        *reinterpret_cast<float4*>(Us + t * DVS + c4) =
+            t < n ? *reinterpret_cast<const float4*>(o + (size_t)t * nH * dv + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const float* sb = ng_after_wait(P.sb) + slot * dk * dv + v0;
+    for (int idx = tid; idx < dk * (DVS / 4); idx += GC_THREADS) {
+        const int d = idx / (DVS / 4), c4 = (idx % (DVS / 4)) * 4;
+        *reinterpret_cast<float4*>(Ss + d * DVS + c4) = *reinterpret_cast<const float4*>(sb + (size_t)d * dv + c4);
+    }
+    __syncthreads();
+    {   // scores inside the chunk: a 2 x 4 tile per thread
+        const int i0 = (tid / 8) * 2, j0 = (tid % 8) * 4;
+        float a[2][4] = {};
+        if (j0 <= i0 + 1) {
+            for (int d = 0; d < dk; ++d) {
+                const float qa = Qs[i0 * ldk + d], qb = Qs[(i0 + 1) * ldk + d];
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    const float kv = Ks[(j0 + cc) * ldk + d];
+                    a[0][cc] = fmaf(qa, kv, a[0][cc]);
+                    a[1][cc] = fmaf(qb, kv, a[1][cc]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                const int i = i0 + r, j = j0 + cc;
+                Ps[i * ldp + j] = j <= i ? a[r][cc] * expf(cl[i] - cl[j]) : 0.f;
+            }
+    }
+    __syncthreads();
+    // o: 4 x 2 tiles over GC x DVS; inside the chunk (P U) and from the state (Q S), kept apart until the end
+    for (int tile = tid; tile < (GC / 4) * (DVS / 2); tile += GC_THREADS) {
+        const int i0 = (tile / (DVS / 2)) * 4, c0 = (tile % (DVS / 2)) * 2;
+        float in[4][2] = {}, st[4][2] = {};
+        for (int j = 0; j < GC; ++j) {
+            const float2 uv = *reinterpret_cast<const float2*>(Us + j * DVS + c0);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const float pv = Ps[(i0 + r) * ldp + j];
+                in[r][0] = fmaf(pv, uv.x, in[r][0]);
+                in[r][1] = fmaf(pv, uv.y, in[r][1]);
+            }
+        }
+        for (int d = 0; d < dk; ++d) {
+            const float2 sv = *reinterpret_cast<const float2*>(Ss + d * DVS + c0);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const float qv = Qs[(i0 + r) * ldk + d];
+                st[r][0] = fmaf(qv, sv.x, st[r][0]);
+                st[r][1] = fmaf(qv, sv.y, st[r][1]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int i = i0 + r;
+            if (i < n) {
+                const float g = expf(cl[i]);
+                *reinterpret_cast<float2*>(o + (size_t)i * nH * dv + c0) = make_float2(in[r][0] + g * st[r][0], in[r][1] + g * st[r][1]);
+            }
+        }
+    }
+}
+
+static inline size_t gc_prep_smem(int dk, int dv) { return ((size_t)GC * (dk + 1) + GC * GC + 2 * GC + GC * dv) * sizeof(float); }
+static inline size_t gc_scan_smem(int dk) {
+    return ((size_t)2 * (2 * GC * dk + GC * GC_DVS) + dk * GC_DVS + GC * GC_DVS + GC_THREADS * GC_RED) * sizeof(float);
+}
+static inline int gc_out_slice(int dv) { return dv % 32 == 0 ? 32 : 16; }
+static inline size_t gc_out_smem(int dk, int dv) {
+    const int dvs = gc_out_slice(dv);
+    return ((size_t)2 * GC * (dk + 1) + GC * dvs + GC * (GC + 1) + GC + dk * dvs) * sizeof(float);
+}
+
+// Whether the chunked kernels take these head sizes: key rows in fours, at most 256; value columns in sixteens.
+NG_EXPORT int ng_gd_chunked_takes(int dk, int dv) {
+    return dk > 0 && dk % 4 == 0 && dk <= 256 && dv > 0 && dv % GC_DVS == 0;
+}
+
+// float32 values of the chunked kernels' scratch for a step of n_rows rows in n_entries entries
+NG_EXPORT long long ng_gd_chunked_scratch(int n_rows, int n_entries, int nH, int dk, int dv) {
+    return ((long long)n_rows / GC + n_entries + 1) * nH * ((long long)2 * GC * dk + GC + (long long)dk * dv);
+}
+
+// As ng_gated_delta for steps with long portions; `scratch`: ng_gd_chunked_scratch float32 values, 16-byte aligned.
+NG_EXPORT int ng_gated_delta_chunked(const float* conv, const void* p, int ldp, int off_a, int off_b, const float* a_log,
+                                     const float* dt_bias, float* state, float* o_raw, float* scratch, const int* cu_q,
+                                     const int* ctx_before, const int* slots, int n_entries, int n_rows, int max_q, int nH,
+                                     int nG, int dk, int dv, int act_bf16, cudaStream_t stream) {
+    if (n_entries <= 0 || n_rows <= 0 || max_q <= 0) return NG_OK;
+    if (nH <= 0 || nG <= 0 || nH % nG || !ng_gd_chunked_takes(dk, dv) || !scratch || ((uintptr_t)scratch & 15) ||
+        ((uintptr_t)o_raw & 15) || ((uintptr_t)state & 15))
+        return NG_BAD_SIZE;
+    const size_t n_slots = (size_t)n_rows / GC + n_entries + 1;
+    GcParams P;
+    P.conv = conv, P.p = p, P.ldp = ldp, P.off_a = off_a, P.off_b = off_b, P.a_log = a_log, P.dt_bias = dt_bias;
+    P.state = state, P.o_raw = o_raw;
+    P.wt = scratch;
+    P.kt = P.wt + n_slots * nH * GC * dk;
+    P.cl = P.kt + n_slots * nH * GC * dk;
+    P.sb = P.cl + n_slots * nH * GC;
+    P.cu_q = cu_q, P.ctx_before = ctx_before, P.slots = slots;
+    P.nH = nH, P.nG = nG, P.dk = dk, P.dv = dv, P.dvs = gc_out_slice(dv);
+    const size_t sp = gc_prep_smem(dk, dv), ss = gc_scan_smem(dk), so = gc_out_smem(dk, dv);
+    static bool configured = false;
+    if (!configured) {
+        const int cap = 200 * 1024;
+        if (cudaFuncSetAttribute(gd_chunk_prep_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
+            cudaFuncSetAttribute(gd_chunk_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
+            cudaFuncSetAttribute(gd_chunk_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
+            cudaFuncSetAttribute(gd_chunk_scan_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
+            cudaFuncSetAttribute(gd_chunk_out_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
+            cudaFuncSetAttribute(gd_chunk_out_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess)
+            return NG_LAUNCH_FAILED;
+        configured = true;
+    }
+    if (sp > 200 * 1024 || ss > 200 * 1024 || so > 200 * 1024) return NG_BAD_SIZE;
+    const unsigned chunks = (unsigned)((max_q + GC - 1) / GC);
+    dim3 pgrid(chunks, nH, n_entries), sgrid(dv / GC_DVS, nH, n_entries), ogrid(chunks, nH * (dv / P.dvs), n_entries);
+    if (nH > 65535 || n_entries > 65535 || ogrid.y > 65535) return NG_BAD_SIZE;
+    if (act_bf16) NG_LAUNCH((gd_chunk_prep_kernel<__nv_bfloat16>), pgrid, GC_THREADS, sp, stream, P);
+    else NG_LAUNCH((gd_chunk_prep_kernel<float>), pgrid, GC_THREADS, sp, stream, P);
+    if (dk <= 128) NG_LAUNCH((gd_chunk_scan_kernel<1>), sgrid, GC_THREADS, ss, stream, P);
+    else NG_LAUNCH((gd_chunk_scan_kernel<2>), sgrid, GC_THREADS, ss, stream, P);
+    if (P.dvs == 32) NG_LAUNCH((gd_chunk_out_kernel<32>), ogrid, GC_THREADS, so, stream, P);
+    else NG_LAUNCH((gd_chunk_out_kernel<16>), ogrid, GC_THREADS, so, stream, P);
+    return ng_launch_status();
+}

@@ -692,14 +692,17 @@ def gated_delta(p: torch.Tensor, conv_weight: torch.Tensor, a_log: torch.Tensor,
                 norm_weight: torch.Tensor, conv_state: torch.Tensor, state: torch.Tensor, conv_out: torch.Tensor,
                 o_raw: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, ctx_before: torch.Tensor, slots: torch.Tensor,
                 row_entry: torch.Tensor, n_entries: int, max_q: int, n_heads: int, n_qk_heads: int, key_dim: int,
-                value_dim: int, eps: float) -> None:
+                value_dim: int, eps: float, chunk_scratch: torch.Tensor | None = None) -> None:
     """p[N, C + nH*dv + 2*nH] = q (nG*dk) | k (nG*dk) | v (nH*dv) | gate (nH*dv) | a (nH) | b (nH), C the first three.
     The q, k, v channels pass a causal convolution per channel (conv_weight float32 [C, L], tap L-1 on the current
     token; conv_state [slots, L-1, C] float32 carries a request's last inputs) and silu; q and k become unit vectors
     per head, q times dk^(-1/2); beta = sigmoid(b), g = exp(-exp(a_log) * softplus(a + dt_bias)); per value head
     (query/key head h // (nH / nG)):  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q, with
     state[slots, nH, dk, dv] float32; out[N, nH*dv] = o / rms(o) * norm_weight * silu(gate).  ``conv_out``
-    (float32 [N, C]) and ``o_raw`` (float32 [N, nH*dv]) are scratch.  Everything after the projections is float32."""
+    (float32 [N, C]) and ``o_raw`` (float32 [N, nH*dv]) are scratch.  Everything after the projections is float32.
+    With ``chunk_scratch`` (``gated_delta_chunked_scratch`` float32 values) the recurrence runs chunk by chunk, most of
+    a portion's work side by side (``gated_delta_chunked_takes`` tells whether the kernels take the head sizes); else
+    token by token.  The two differ by rounding only."""
     n = p.shape[0]
     C = (2 * n_qk_heads * key_dim) + n_heads * value_dim
     ldp = C + n_heads * value_dim + 2 * n_heads
@@ -717,14 +720,36 @@ def gated_delta(p: torch.Tensor, conv_weight: torch.Tensor, a_log: torch.Tensor,
     f = _fn("gated_delta", "ng_gd_conv_silu", [_c_void_p, _c_int] + [_c_void_p] * 6 + [_c_int] * 5 + [_c_void_p])
     _check(f(_ptr(p), ldp, _ptr(conv_weight), _ptr(conv_state), _ptr(conv_out), _ptr(cu_q), _ptr(ctx_before), _ptr(slots),
              n_entries, int(max_q), C, L, act, _stream()), "gated_delta (convolution)")
-    f = _fn("gated_delta", "ng_gated_delta", [_c_void_p, _c_void_p] + [_c_int] * 3 + [_c_void_p] * 7 + [_c_int] * 6 + [_c_void_p])
-    _check(f(_ptr(conv_out), _ptr(p), ldp, C + n_heads * value_dim, C + n_heads * value_dim + n_heads, _ptr(a_log),
-             _ptr(dt_bias), _ptr(state), _ptr(o_raw), _ptr(cu_q), _ptr(ctx_before), _ptr(slots), n_entries, n_heads,
-             n_qk_heads, key_dim, value_dim, act, _stream()), "gated_delta")
+    if chunk_scratch is not None:
+        need = gated_delta_chunked_scratch(n, n_entries, n_heads, key_dim, value_dim)
+        _f32(chunk_scratch, "chunk scratch")
+        if chunk_scratch.numel() < need or not gated_delta_chunked_takes(key_dim, value_dim):
+            raise KernelError(f"gated_delta: the chunked kernels need {need} float32 values of scratch and head sizes they take")
+        f = _fn("gated_delta", "ng_gated_delta_chunked", [_c_void_p, _c_void_p] + [_c_int] * 3 + [_c_void_p] * 8 + [_c_int] * 8
+                + [_c_void_p])
+        _check(f(_ptr(conv_out), _ptr(p), ldp, C + n_heads * value_dim, C + n_heads * value_dim + n_heads, _ptr(a_log),
+                 _ptr(dt_bias), _ptr(state), _ptr(o_raw), _ptr(chunk_scratch), _ptr(cu_q), _ptr(ctx_before), _ptr(slots),
+                 n_entries, n, int(max_q), n_heads, n_qk_heads, key_dim, value_dim, act, _stream()), "gated_delta (chunked)")
+    else:
+        f = _fn("gated_delta", "ng_gated_delta", [_c_void_p, _c_void_p] + [_c_int] * 3 + [_c_void_p] * 7 + [_c_int] * 6
+                + [_c_void_p])
+        _check(f(_ptr(conv_out), _ptr(p), ldp, C + n_heads * value_dim, C + n_heads * value_dim + n_heads, _ptr(a_log),
+                 _ptr(dt_bias), _ptr(state), _ptr(o_raw), _ptr(cu_q), _ptr(ctx_before), _ptr(slots), n_entries, n_heads,
+                 n_qk_heads, key_dim, value_dim, act, _stream()), "gated_delta")
     f = _fn("gated_delta", "ng_gd_finish", [_c_void_p, _c_void_p, _c_int, _c_int] + [_c_void_p] * 3 + [_c_int] * 3
             + [_c_float, _c_int, _c_void_p])
     _check(f(_ptr(o_raw), _ptr(p), ldp, C, _ptr(norm_weight), _ptr(row_entry), _ptr(out), n, n_heads, value_dim, float(eps),
              act, _stream()), "gated_delta (head norm)")
+
+
+def gated_delta_chunked_scratch(n_rows: int, n_entries: int, n_heads: int, key_dim: int, value_dim: int) -> int:
+    """float32 values the chunked gated delta kernels need for the chunks' tiles and states."""
+    return (n_rows // 32 + n_entries + 1) * n_heads * (64 * key_dim + 32 + key_dim * value_dim)
+
+
+def gated_delta_chunked_takes(key_dim: int, value_dim: int) -> bool:
+    f = _fn("gated_delta", "ng_gd_chunked_takes", [_c_int, _c_int])
+    return bool(f(int(key_dim), int(value_dim)))
 
 
 # ----------------------------------------------------------------------------- small parts of a layer or a model

@@ -22,6 +22,7 @@ class GatedDelta:
     taps - 1 inputs [taps - 1, channels] float32; the mixer declares the two needs and is handed the two views."""
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
+    CHUNKED_MIN_ROWS = 64  # a bfloat16 step whose longest portion has this many tokens runs the chunk-by-chunk kernels
 
     def __init__(self, spec, *, dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device
@@ -61,8 +62,17 @@ class GatedDelta:
     def kernels(self):
         return [("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None), ("gated_delta", None)]
 
+    def _chunked(self):
+        s = self.spec
+        # the head sizes the chunked kernels take: key rows in fours, at most 256; value columns in sixteens
+        return self.dtype == torch.bfloat16 and s.key_dim % 4 == 0 and s.key_dim <= 256 and s.value_dim % 16 == 0
+
     def scratch_bytes_per_row(self):
-        return 4 * (self.channels + self.spec.n_heads * self.spec.value_dim)
+        s = self.spec
+        per_row = 4 * (self.channels + s.n_heads * s.value_dim)
+        if self._chunked():
+            per_row += 4 * s.n_heads * (64 * s.key_dim + 32 + s.key_dim * s.value_dim) // 32
+        return per_row
 
     def forward(self, x, ctx, cache, out_name="mixer_out"):
         s = self.spec
@@ -73,7 +83,15 @@ class GatedDelta:
         conv = ctx.ws.buf("gd_conv", n, self.channels, torch.float32)
         o_raw = ctx.ws.buf("gd_raw", n, s.n_heads * s.value_dim, torch.float32)
         o = ctx.ws.buf("gd_out", n, s.n_heads * s.value_dim, self.dtype)
+        # float32 keeps the token-by-token kernel for every step: there a token's arithmetic is the same however its
+        # request is cut.  bfloat16 steps with a long portion regroup the recurrence chunk by chunk (still float32).
+        chunks = None
+        if ctx.max_q >= self.CHUNKED_MIN_ROWS and self._chunked():
+            need = ops.gated_delta_chunked_scratch(n, ctx.n_entries, s.n_heads, s.key_dim, s.value_dim)
+            bound = ops.gated_delta_chunked_scratch(ctx.ws.max_rows, ctx.ws.max_rows // self.CHUNKED_MIN_ROWS + 64,
+                                                    s.n_heads, s.key_dim, s.value_dim)
+            chunks = ctx.ws.flat("gd_chunks", need, torch.float32, reserve=max(need, bound))
         ops.gated_delta(p, self.w_conv, self.a_log, self.dt_bias, self.norm, conv_state.state, state.state, conv, o_raw, o,
                         ctx.cu_q, ctx.ctx_before, ctx.slots, ctx.row_entry, ctx.n_entries, ctx.max_q, s.n_heads,
-                        s.n_qk_heads, s.key_dim, s.value_dim, s.eps)
+                        s.n_qk_heads, s.key_dim, s.value_dim, s.eps, chunk_scratch=chunks)
         return ops.linear_to_residual(o, self.w_o, None, ctx.ws, out_name, residual=ctx.residual)

@@ -162,7 +162,7 @@ def mapped_attention(q, k_pages, v_pages, table, positions, row_entry, out, n_he
 
 
 def gated_delta(p, conv_weight, a_log, dt_bias, norm_weight, conv_state, state, conv_out, o_raw, out, cu_q, ctx_before, slots,
-                row_entry, n_entries, max_q, n_heads, n_qk_heads, key_dim, value_dim, eps):
+                row_entry, n_entries, max_q, n_heads, n_qk_heads, key_dim, value_dim, eps, chunk_scratch=None):
     nH, nG, dk, dv = n_heads, n_qk_heads, key_dim, value_dim
     C = 2 * nG * dk + nH * dv
     L = conv_weight.shape[1]

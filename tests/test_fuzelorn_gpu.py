@@ -347,6 +347,73 @@ def test_gated_delta_rule_batch_of_unequal_entries(dtype):
         assert rel_err(torch.cat(got[i]), want[i]) < TOL[dtype], i
 
 
+def _gd_op(o, p, w, state, conv_state, lens, before, slots, nH, nG, dk, dv, chunked):
+    """The launcher alone on float32 rows: outputs, with the states updated in place."""
+    n, C = p.shape[0], 2 * nG * dk + nH * dv
+    cu = [0]
+    for q in lens:
+        cu.append(cu[-1] + q)
+    re = [e for e, q in enumerate(lens) for _ in range(q)]
+    conv = torch.empty(n, C, device=DEV)
+    raw = torch.empty(n, nH * dv, device=DEV)
+    out = torch.empty(n, nH * dv, device=DEV)
+    scratch = None
+    if chunked:
+        scratch = torch.full((o.gated_delta_chunked_scratch(n, len(lens), nH, dk, dv),), float("nan"), device=DEV)
+    o.gated_delta(p, w["conv"], w["a_log"], w["dt_bias"], w["norm"], conv_state, state, conv, raw, out, _i32(cu), _i32(before),
+                  _i32(slots), _i32(re), len(lens), max(lens), nH, nG, dk, dv, 1e-5, chunk_scratch=scratch)
+    return out
+
+
+@pytest.mark.parametrize("nH,nG,dk,dv,taps", [(4, 2, 64, 32, 3), (2, 1, 128, 128, 4), (2, 2, 256, 48, 2), (3, 1, 20, 16, 4),
+                                              (8, 4, 128, 64, 4)])
+def test_gated_delta_rule_chunk_by_chunk_equals_token_by_token(nH, nG, dk, dv, taps):
+    """The regrouped recurrence against the token-by-token one, both float32, over entries whose lengths fall on, just
+    under and just over a chunk's edge, beside single tokens; requests that go on start from states of size, not zero;
+    a second step goes on from the states the first one left.  Heads from nearly no decay to forgetful ones."""
+    o = ops()
+    assert o.gated_delta_chunked_takes(dk, dv) and not o.gated_delta_chunked_takes(dk + 1, dv)
+    g = torch.Generator().manual_seed(dk + dv)
+    C = 2 * nG * dk + nH * dv
+    w = {"conv": (0.6 * torch.randn(C, taps, generator=g)).to(DEV), "a_log": torch.linspace(-6.0, 0.5, nH).to(DEV),
+         "dt_bias": (0.5 * torch.randn(nH, generator=g)).to(DEV), "norm": (1 + 0.2 * torch.randn(dv, generator=g)).to(DEV)}
+    states = (0.3 * torch.randn(6, nH, dk, dv, generator=g)).to(DEV)
+    convs = torch.randn(6, taps - 1, C, generator=g).to(DEV)
+    steps = [([130, 1, 64, 33, 7, 95], [0, 12, 5, 0, 3, 40], [4, 1, 0, 5, 2, 3]), ([63, 32, 1, 65, 31, 2], [130, 13, 69, 33, 10, 135], [4, 1, 0, 5, 2, 3])]
+    got = {}
+    for chunked in (False, True):
+        st, cs, outs = states.clone(), convs.clone(), []
+        for i, (lens, before, slots) in enumerate(steps):
+            gp = torch.Generator().manual_seed(100 + i)
+            p = (1.5 * torch.randn(sum(lens), C + nH * dv + 2 * nH, generator=gp)).to(DEV)
+            outs.append(_gd_op(o, p, w, st, cs, lens, before, slots, nH, nG, dk, dv, chunked))
+        got[chunked] = (torch.cat(outs), st, cs)
+    assert torch.isfinite(got[True][0]).all()
+    assert rel_err(got[True][0], got[False][0]) < 2e-5
+    assert rel_err(got[True][1], got[False][1]) < 2e-5
+    assert torch.equal(got[True][2], got[False][2])
+
+
+def test_gated_delta_rule_long_portions_in_chunks():
+    """A bfloat16 part over portions long enough for the chunk-by-chunk kernels, short ones between them, against the
+    plain statement: the state passes from one kind of kernel to the other at every cut."""
+    D, T, Hr, Gr, dk, dv, taps = 48, 420, 4, 2, 64, 32, 4
+    part = build("mixer", GatedDeltaSpec(hidden=D, n_heads=Hr, n_qk_heads=Gr, key_dim=dk, value_dim=dv, taps=taps, eps=1e-5),
+                 dtype=torch.bfloat16, device=DEV)
+    w = _draw(part, 9)
+    x = _x((T, D), torch.bfloat16)
+    m = {"heads": Hr, "kv_heads": Gr, "dim": dk, "vdim": dv, "conv": taps}
+    want = plain.right_mixer(x.double().cpu(), w, "m.", m, 1e-5)
+    views = _gd_state(part, 3)
+    cuts, at = [], 0
+    for n in [97, 2, 64, 33, 129, 1, 94]:
+        cuts.append((at, n))
+        at += n
+    assert at == T
+    assert rel_err(_run_gd(part, x, cuts, torch.bfloat16, views, slot=2), want) < TOL[torch.bfloat16]
+    assert rel_err(_run_gd(part, x, [(0, T)], torch.bfloat16, views, slot=2), want) < TOL[torch.bfloat16]
+
+
 # ------------------------------------------------------------------------------------------ the two mixers side by side
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("accumulate", [False, True])
