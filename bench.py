@@ -956,7 +956,7 @@ def fuzelorn_config(width, layers):
            "expert": {"ff": width // 4, "limit": 7.0}, "shared": {"ff": width // 2, "limit": 7.0}}
     dense = {"kind": "dense", "ff": 4 * width}
     return {"architecture": "Fuzelorn", "vocab": 65536, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
-            "embedding": {"scale": 0.5, "bigram": {"buckets": 100003, "mul_prev": 31, "mul_cur": 17}},
+            "embedding": {"scale": 2.0, "bigram": {"buckets": 100003, "mul_prev": 36313, "mul_cur": 27191}},
             "layers": [{"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": dense if i == 0 else moe}
                        for i in range(layers)]}
 

@@ -301,13 +301,15 @@ NG_EXPORT int ng_gd_finish(const float* o_raw, const void* p, int ldp, int off_g
 // thread per column, and leaves W (transposed), K~ and cl in the scratch and U' where the outputs will be.  `scan` (a
 // block per request, head and 16 value columns) walks the chunks in order: U = U' - W S in place, S' from K~ and U; the
 // state before each chunk goes to the scratch; the next chunk's tiles are copied asynchronously meanwhile.  `out` (a
-// block per chunk, head and slice of value columns) forms o from q, k, cl, U and the chunk's S, in U's place.
+// block per chunk and head) forms o from q, k, cl, U and the chunk's S, in U's place.
 // Float32 FFMA throughout; the results differ from the token-by-token kernel's by rounding only.  Chunk c of entry e
 // uses slot cu_q[e] / GC + e + c of the scratch, as the chunks of different entries then never meet.
 #define GC 32
 #define GC_THREADS 128
 #define GC_DVS 16          // value columns of a scan block
 #define GC_RED 20          // floats between two threads' partial tiles (no bank conflicts for 16-byte accesses)
+#define GC_LDT 36          // floats between the rows of a transposed tile [dim][GC]: 16-byte rows, and a quarter warp's
+                           // 16-byte accesses to one column of four tokens meet every bank once
 
 struct GcParams {
     const float* conv; const void* p;
@@ -319,7 +321,7 @@ struct GcParams {
     float* cl;              // [slots][nH][GC]
     float* sb;              // [slots][nH][dk][dv]: the state before each chunk
     const int* cu_q; const int* ctx_before; const int* slots;
-    int nH, nG, dk, dv, dvs;
+    int nH, nG, dk, dv;
 };
 
 // rows of unit vectors into shared memory [GC][dk+1]: all loads first (many in flight), then a warp per row for the
@@ -606,22 +608,48 @@ gd_chunk_scan_kernel(const GcParams P) {
     }
 }
 
-template <int DVS>
+// rows of unit vectors, transposed, into shared memory [dk][GC_LDT] (dst[i][t] = x_t[i]): a warp takes four rows at
+// a time, a lane every 32nd coordinate of each; the rows' sums of squares first, then the rows again (from L1), scaled,
+// four tokens of a coordinate in one 16-byte store; rows past n are zero.  Ends with the block in step.
+__device__ __forceinline__ void gc_load_unit_t(const float* __restrict__ src, size_t ld, int n, int dk, float mul, float* dst) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int t0 = warp * 4; t0 < GC; t0 += (GC_THREADS / 32) * 4) {
+        float ss[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i = lane; i < dk; i += 32) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const float x = t0 + r < n ? src[(size_t)(t0 + r) * ld + i] : 0.f;
+                ss[r] = fmaf(x, x, ss[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) ss[r] = rsqrtf(ng_warp_sum(ss[r]) + 1e-6f) * mul;
+        for (int i = lane; i < dk; i += 32) {
+            float x[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) x[r] = t0 + r < n ? src[(size_t)(t0 + r) * ld + i] * ss[r] : 0.f;
+            *reinterpret_cast<float4*>(dst + i * GC_LDT + t0) = make_float4(x[0], x[1], x[2], x[3]);
+        }
+    }
+    __syncthreads();
+}
+
+// A block per chunk and head.  q and k lie transposed in shared memory, so that a thread's eight tokens of a coordinate
+// are two 16-byte reads; the state before the chunk and U are read from global memory as they are needed (a warp
+// reads whole rows' segments), four value columns a thread.  U's place is overwritten with o, so a pass of tiles
+// (all eight-token groups of its columns) is read whole before any of it is written.
 __global__ void __launch_bounds__(GC_THREADS)
 gd_chunk_out_kernel(const GcParams P) {
     extern __shared__ float4 sm_aligned[];
     float* sm = reinterpret_cast<float*>(sm_aligned);
-    const int dk = P.dk, dv = P.dv, nH = P.nH, ldk = dk + 1, ldp = GC + 1;
-    float* Qs = sm;                        // [GC][dk+1]
-    float* Ks = Qs + GC * ldk;             // [GC][dk+1]
-    float* Us = Ks + GC * ldk;             // [GC][DVS]
-    float* Ps = Us + GC * DVS;             // [GC][GC+1]
-    float* cl = Ps + GC * ldp;             // [GC]
-    float* Ss = cl + GC;                   // [dk][DVS]
+    const int dk = P.dk, dv = P.dv, nH = P.nH;
+    float* Qt = sm;                        // [dk][GC_LDT]
+    float* Kt = Qt + dk * GC_LDT;          // [dk][GC_LDT]
+    float* Pt = Kt + dk * GC_LDT;          // [GC][GC_LDT]: Pt[j][i] = exp(cl_i - cl_j) (q_i . k_j), j <= i
+    float* cl = Pt + GC * GC_LDT;          // [GC]
     ng_pdl_trigger();
     ng_pdl_wait();
-    const int c = blockIdx.x, e = blockIdx.z, slices = dv / DVS;
-    const int head = blockIdx.y / slices, v0 = (blockIdx.y % slices) * DVS;
+    const int c = blockIdx.x, head = blockIdx.y, e = blockIdx.z;
     const int q0 = P.cu_q[e], qlen = P.cu_q[e + 1] - q0;
     if (c * GC >= qlen) return;
     const int n = min(GC, qlen - c * GC), row0 = q0 + c * GC;
@@ -630,73 +658,78 @@ gd_chunk_out_kernel(const GcParams P) {
     const int C = 2 * P.nG * dk + nH * dv;
     const size_t off_q = (size_t)(head / (nH / P.nG)) * dk, off_k = (size_t)P.nG * dk + off_q;
     const float* conv = ng_after_wait(P.conv) + (size_t)row0 * C;
-    gc_load_unit(conv + off_q, C, n, dk, rsqrtf((float)dk), Qs);
-    gc_load_unit(conv + off_k, C, n, dk, 1.f, Ks);
     if (tid < GC) cl[tid] = ng_after_wait(P.cl)[slot * GC + tid];
-    float* o = ng_after_wait(P.o_raw) + (size_t)row0 * nH * dv + (size_t)head * dv + v0;
-    for (int idx = tid; idx < GC * (DVS / 4); idx += GC_THREADS) {
-        const int t = idx / (DVS / 4), c4 = (idx % (DVS / 4)) * 4;
-        *reinterpret_cast<float4*>(Us + t * DVS + c4) =
-            t < n ? *reinterpret_cast<const float4*>(o + (size_t)t * nH * dv + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    const float* sb = ng_after_wait(P.sb) + slot * dk * dv + v0;
-    for (int idx = tid; idx < dk * (DVS / 4); idx += GC_THREADS) {
-        const int d = idx / (DVS / 4), c4 = (idx % (DVS / 4)) * 4;
-        *reinterpret_cast<float4*>(Ss + d * DVS + c4) = *reinterpret_cast<const float4*>(sb + (size_t)d * dv + c4);
-    }
-    __syncthreads();
-    {   // scores inside the chunk: a 2 x 4 tile per thread
-        const int i0 = (tid / 8) * 2, j0 = (tid % 8) * 4;
+    gc_load_unit_t(conv + off_q, C, n, dk, rsqrtf((float)dk), Qt);
+    gc_load_unit_t(conv + off_k, C, n, dk, 1.f, Kt);
+    {   // scores inside the chunk: four queries x two keys a thread
+        const int i4 = (tid & 7) * 4, j2 = (tid >> 3) * 2;
         float a[2][4] = {};
-        if (j0 <= i0 + 1) {
+        if (j2 <= i4 + 3) {
+#pragma unroll 4
             for (int d = 0; d < dk; ++d) {
-                const float qa = Qs[i0 * ldk + d], qb = Qs[(i0 + 1) * ldk + d];
+                const float4 q4 = *reinterpret_cast<const float4*>(Qt + d * GC_LDT + i4);
+                const float2 k2 = *reinterpret_cast<const float2*>(Kt + d * GC_LDT + j2);
+                const float qv[4] = {q4.x, q4.y, q4.z, q4.w}, kv[2] = {k2.x, k2.y};
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    const float kv = Ks[(j0 + cc) * ldk + d];
-                    a[0][cc] = fmaf(qa, kv, a[0][cc]);
-                    a[1][cc] = fmaf(qb, kv, a[1][cc]);
-                }
+                for (int r = 0; r < 2; ++r)
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) a[r][cc] = fmaf(kv[r], qv[cc], a[r][cc]);
             }
         }
 #pragma unroll
-        for (int r = 0; r < 2; ++r)
+        for (int r = 0; r < 2; ++r) {
+            const int j = j2 + r;
+            float w[4];
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                const int i = i0 + r, j = j0 + cc;
-                Ps[i * ldp + j] = j <= i ? a[r][cc] * expf(cl[i] - cl[j]) : 0.f;
-            }
+            for (int cc = 0; cc < 4; ++cc) w[cc] = j <= i4 + cc ? a[r][cc] * expf(cl[i4 + cc] - cl[j]) : 0.f;
+            *reinterpret_cast<float4*>(Pt + j * GC_LDT + i4) = make_float4(w[0], w[1], w[2], w[3]);
+        }
     }
     __syncthreads();
-    // o: 4 x 2 tiles over GC x DVS; inside the chunk (P U) and from the state (Q S), kept apart until the end
-    for (int tile = tid; tile < (GC / 4) * (DVS / 2); tile += GC_THREADS) {
-        const int i0 = (tile / (DVS / 2)) * 4, c0 = (tile % (DVS / 2)) * 2;
-        float in[4][2] = {}, st[4][2] = {};
-        for (int j = 0; j < GC; ++j) {
-            const float2 uv = *reinterpret_cast<const float2*>(Us + j * DVS + c0);
+    const float* sb = ng_after_wait(P.sb) + slot * dk * dv;
+    float* o = ng_after_wait(P.o_raw) + (size_t)row0 * nH * dv + (size_t)head * dv;
+    const size_t ldo = (size_t)nH * dv;
+    for (int base = 0; base < dv; base += GC_THREADS) {      // dv tiles: (dv / 4 column groups) x (four groups of eight tokens)
+        const int tile = base + tid, t8 = (tile & 3) * 8, c0 = (tile >> 2) * 4;
+        const bool active = c0 < dv;
+        float acc[8][4] = {};
+        if (active) {
+#pragma unroll 4
+            for (int d = 0; d < dk; ++d) {       // from the state: Q S
+                const float4 s4 = *reinterpret_cast<const float4*>(sb + (size_t)d * dv + c0);
+                const float4 qa = *reinterpret_cast<const float4*>(Qt + d * GC_LDT + t8);
+                const float4 qb = *reinterpret_cast<const float4*>(Qt + d * GC_LDT + t8 + 4);
+                const float qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                const float pv = Ps[(i0 + r) * ldp + j];
-                in[r][0] = fmaf(pv, uv.x, in[r][0]);
-                in[r][1] = fmaf(pv, uv.y, in[r][1]);
+                for (int r = 0; r < 8; ++r)
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) acc[r][cc] = fmaf(qv[r], sv[cc], acc[r][cc]);
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const float g = expf(cl[t8 + r]);
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) acc[r][cc] *= g;
+            }
+            const int j1 = min(n, t8 + 8);       // inside the chunk: P U, the keys up to the group's last token
+#pragma unroll 4
+            for (int j = 0; j < j1; ++j) {
+                const float4 u4 = *reinterpret_cast<const float4*>(o + (size_t)j * ldo + c0);
+                const float4 pa = *reinterpret_cast<const float4*>(Pt + j * GC_LDT + t8);
+                const float4 pb = *reinterpret_cast<const float4*>(Pt + j * GC_LDT + t8 + 4);
+                const float pv[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w}, uv[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+                for (int r = 0; r < 8; ++r)
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) acc[r][cc] = fmaf(pv[r], uv[cc], acc[r][cc]);
             }
         }
-        for (int d = 0; d < dk; ++d) {
-            const float2 sv = *reinterpret_cast<const float2*>(Ss + d * DVS + c0);
+        __syncthreads();                         // every read of this pass's columns of U is done
+        if (active) {
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                const float qv = Qs[(i0 + r) * ldk + d];
-                st[r][0] = fmaf(qv, sv.x, st[r][0]);
-                st[r][1] = fmaf(qv, sv.y, st[r][1]);
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int i = i0 + r;
-            if (i < n) {
-                const float g = expf(cl[i]);
-                *reinterpret_cast<float2*>(o + (size_t)i * nH * dv + c0) = make_float2(in[r][0] + g * st[r][0], in[r][1] + g * st[r][1]);
-            }
+            for (int r = 0; r < 8; ++r)
+                if (t8 + r < n)
+                    *reinterpret_cast<float4*>(o + (size_t)(t8 + r) * ldo + c0) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
         }
     }
 }
@@ -705,11 +738,7 @@ static inline size_t gc_prep_smem(int dk, int dv) { return ((size_t)GC * (dk + 1
 static inline size_t gc_scan_smem(int dk) {
     return ((size_t)2 * (2 * GC * dk + GC * GC_DVS) + dk * GC_DVS + GC * GC_DVS + GC_THREADS * GC_RED) * sizeof(float);
 }
-static inline int gc_out_slice(int dv) { return dv % 32 == 0 ? 32 : 16; }
-static inline size_t gc_out_smem(int dk, int dv) {
-    const int dvs = gc_out_slice(dv);
-    return ((size_t)2 * GC * (dk + 1) + GC * dvs + GC * (GC + 1) + GC + dk * dvs) * sizeof(float);
-}
+static inline size_t gc_out_smem(int dk) { return ((size_t)2 * dk * GC_LDT + GC * GC_LDT + GC) * sizeof(float); }
 
 // Whether the chunked kernels take these head sizes: key rows in fours, at most 256; value columns in sixteens.
 NG_EXPORT int ng_gd_chunked_takes(int dk, int dv) {
@@ -739,8 +768,8 @@ NG_EXPORT int ng_gated_delta_chunked(const float* conv, const void* p, int ldp, 
     P.cl = P.kt + n_slots * nH * GC * dk;
     P.sb = P.cl + n_slots * nH * GC;
     P.cu_q = cu_q, P.ctx_before = ctx_before, P.slots = slots;
-    P.nH = nH, P.nG = nG, P.dk = dk, P.dv = dv, P.dvs = gc_out_slice(dv);
-    const size_t sp = gc_prep_smem(dk, dv), ss = gc_scan_smem(dk), so = gc_out_smem(dk, dv);
+    P.nH = nH, P.nG = nG, P.dk = dk, P.dv = dv;
+    const size_t sp = gc_prep_smem(dk, dv), ss = gc_scan_smem(dk), so = gc_out_smem(dk);
     static bool configured = false;
     if (!configured) {
         const int cap = 200 * 1024;
@@ -748,20 +777,18 @@ NG_EXPORT int ng_gated_delta_chunked(const float* conv, const void* p, int ldp, 
             cudaFuncSetAttribute(gd_chunk_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
             cudaFuncSetAttribute(gd_chunk_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
             cudaFuncSetAttribute(gd_chunk_scan_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
-            cudaFuncSetAttribute(gd_chunk_out_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess ||
-            cudaFuncSetAttribute(gd_chunk_out_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess)
+            cudaFuncSetAttribute(gd_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cap) != cudaSuccess)
             return NG_LAUNCH_FAILED;
         configured = true;
     }
     if (sp > 200 * 1024 || ss > 200 * 1024 || so > 200 * 1024) return NG_BAD_SIZE;
     const unsigned chunks = (unsigned)((max_q + GC - 1) / GC);
-    dim3 pgrid(chunks, nH, n_entries), sgrid(dv / GC_DVS, nH, n_entries), ogrid(chunks, nH * (dv / P.dvs), n_entries);
-    if (nH > 65535 || n_entries > 65535 || ogrid.y > 65535) return NG_BAD_SIZE;
+    dim3 pgrid(chunks, nH, n_entries), sgrid(dv / GC_DVS, nH, n_entries), ogrid(chunks, nH, n_entries);
+    if (nH > 65535 || n_entries > 65535) return NG_BAD_SIZE;
     if (act_bf16) NG_LAUNCH((gd_chunk_prep_kernel<__nv_bfloat16>), pgrid, GC_THREADS, sp, stream, P);
     else NG_LAUNCH((gd_chunk_prep_kernel<float>), pgrid, GC_THREADS, sp, stream, P);
     if (dk <= 128) NG_LAUNCH((gd_chunk_scan_kernel<1>), sgrid, GC_THREADS, ss, stream, P);
     else NG_LAUNCH((gd_chunk_scan_kernel<2>), sgrid, GC_THREADS, ss, stream, P);
-    if (P.dvs == 32) NG_LAUNCH((gd_chunk_out_kernel<32>), ogrid, GC_THREADS, so, stream, P);
-    else NG_LAUNCH((gd_chunk_out_kernel<16>), ogrid, GC_THREADS, so, stream, P);
+    NG_LAUNCH(gd_chunk_out_kernel, ogrid, GC_THREADS, so, stream, P);
     return ng_launch_status();
 }

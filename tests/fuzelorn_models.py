@@ -72,7 +72,7 @@ FUZE_U = {
 # one expert, more experts kept than chosen, recurrent heads wider than a warp's share
 FUZE_W = {
     "architecture": "Fuzelorn", "vocab": 90, "width": 64, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
-    "embedding": {"scale": 0.5, "bigram": {"buckets": 7, "mul_prev": 3, "mul_cur": 1}},
+    "embedding": {"scale": 0.75, "bigram": {"buckets": 7, "mul_prev": 3, "mul_cur": 1}},
     "loop": {"start": 0, "stop": 2, "times": 3},
     "layers": [
         _layer(_left(4, 2, 32, 16, 0.2, 70, (0.4, 32)), _right(2, 2, 40, 20, 4), _moe(4, 2, 16, 1.2, (4, 3), (24, 1.0))),
