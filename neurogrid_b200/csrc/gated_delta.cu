@@ -307,6 +307,7 @@ NG_EXPORT int ng_gd_finish(const float* o_raw, const void* p, int ldp, int off_g
 #define GC 32
 #define GC_THREADS 128
 #define GC_DVS 16          // value columns of a scan block
+#define GS_THREADS 256     // threads of a scan block: two warps a scheduler, one hides the other's shared-memory latency
 #define GC_RED 20          // floats between two threads' partial tiles (no bank conflicts for 16-byte accesses)
 #define GC_LDT 36          // floats between the rows of a transposed tile [dim][GC]: 16-byte rows, and a quarter warp's
                            // 16-byte accesses to one column of four tokens meet every bank once
@@ -328,10 +329,13 @@ struct GcParams {
 // norm; rows past n are zero.  Ends with the block in step.
 __device__ __forceinline__ void gc_load_unit(const float* __restrict__ src, size_t ld, int n, int dk, float mul, float* dst) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, ldk = dk + 1;
-#pragma unroll 8
-    for (int idx = threadIdx.x; idx < GC * dk; idx += GC_THREADS) {
-        const int t = idx / dk, i = idx - t * dk;
-        dst[t * ldk + i] = t < n ? src[(size_t)t * ld + i] : 0.f;
+    const int dk4 = dk >> 2;
+#pragma unroll 4
+    for (int idx = threadIdx.x; idx < GC * dk4; idx += GC_THREADS) {      // 16-byte reads: dk, ld and the start in fours
+        const int t = idx / dk4, i = (idx - t * dk4) * 4;
+        const float4 x = t < n ? *reinterpret_cast<const float4*>(src + (size_t)t * ld + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float* d = dst + t * ldk + i;
+        d[0] = x.x, d[1] = x.y, d[2] = x.z, d[3] = x.w;
     }
     __syncthreads();
     for (int t = warp; t < n; t += GC_THREADS / 32) {
@@ -366,10 +370,12 @@ gd_chunk_prep_kernel(const GcParams P) {
     const size_t off_k = (size_t)P.nG * dk + (size_t)(head / (nH / P.nG)) * dk;
     const size_t off_v = 2 * (size_t)P.nG * dk + (size_t)head * dv;
     const float* conv = ng_after_wait(P.conv) + (size_t)row0 * C;
-#pragma unroll 8
-    for (int idx = tid; idx < GC * dv; idx += GC_THREADS) {
-        const int t = idx / dv, v = idx - t * dv;
-        Vs[idx] = t < n ? conv[(size_t)t * C + off_v + v] : 0.f;
+    const int dv4 = dv >> 2;
+#pragma unroll 4
+    for (int idx = tid; idx < GC * dv4; idx += GC_THREADS) {
+        const int t = idx / dv4, v = (idx - t * dv4) * 4;
+        *reinterpret_cast<float4*>(Vs + t * dv + v) =
+            t < n ? *reinterpret_cast<const float4*>(conv + (size_t)t * C + off_v + v) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     gc_load_unit(conv + off_k, C, n, dk, 1.f, Ks);
     if (warp == 0) {
@@ -463,9 +469,9 @@ __device__ __forceinline__ void gc_copy16(float* dst, const float* src) {
 __device__ __forceinline__ void gc_copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void gc_copy_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-// NT: 4 x 4 tiles of the state's slice [dk][GC_DVS] a thread keeps in registers (ceil(dk / 4 * 4 / GC_THREADS))
+// NT: 4 x 2 tiles of the state's slice [dk][GC_DVS] a thread keeps in registers (ceil(dk / 4 * (GC_DVS / 2) / GS_THREADS))
 template <int NT>
-__global__ void __launch_bounds__(GC_THREADS)
+__global__ void __launch_bounds__(GS_THREADS)
 gd_chunk_scan_kernel(const GcParams P) {
     extern __shared__ float4 sm_aligned[];
     float* sm = reinterpret_cast<float*>(sm_aligned);
@@ -474,7 +480,7 @@ gd_chunk_scan_kernel(const GcParams P) {
     float* tiles = sm;                               // two of them
     float* Ss = tiles + 2 * per;                     // [dk][GC_DVS]
     float* Us = Ss + dk * GC_DVS;                    // [GC][GC_DVS]
-    float* red = Us + GC * GC_DVS;                   // [4 warps][32 lanes][GC_RED]
+    float* red = Us + GC * GC_DVS;                   // [warps][32 lanes][GC_RED]
     ng_pdl_trigger();
     ng_pdl_wait();
     const int v0 = blockIdx.x * GC_DVS, head = blockIdx.y, e = blockIdx.z;
@@ -489,17 +495,18 @@ gd_chunk_scan_kernel(const GcParams P) {
     const float* cl_all = ng_after_wait(P.cl);
     float* St = P.state + ((size_t)P.slots[e] * nH + head) * dk * dv + v0;
     const bool carried = P.ctx_before[e] > 0;
-    const int cg4 = (tid & 3) * 4;                   // the thread's four value columns, in both products
-    float s[NT][4][4];
+    const int cg2 = (tid & 7) * 2;                   // the thread's two value columns of the state and of U
+    const int cg4 = (lane & 3) * 4;                  // its four columns in W S
+    float s[NT][4][2];
 #pragma unroll
     for (int m = 0; m < NT; ++m) {
-        const int i0 = ((tid + m * GC_THREADS) >> 2) * 4;
+        const int i0 = ((tid + m * GS_THREADS) >> 3) * 4;
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (carried && i0 + r < dk) v = *reinterpret_cast<const float4*>(St + (size_t)(i0 + r) * dv + cg4);
-            s[m][r][0] = v.x, s[m][r][1] = v.y, s[m][r][2] = v.z, s[m][r][3] = v.w;
-            if (i0 + r < dk) *reinterpret_cast<float4*>(Ss + (i0 + r) * GC_DVS + cg4) = v;
+            float2 v = make_float2(0.f, 0.f);
+            if (carried && i0 + r < dk) v = *reinterpret_cast<const float2*>(St + (size_t)(i0 + r) * dv + cg2);
+            s[m][r][0] = v.x, s[m][r][1] = v.y;
+            if (i0 + r < dk) *reinterpret_cast<float2*>(Ss + (i0 + r) * GC_DVS + cg2) = v;
         }
     }
     auto fetch = [&](int c) {
@@ -507,13 +514,13 @@ gd_chunk_scan_kernel(const GcParams P) {
         const size_t slot = slot0 + (size_t)c * nH;
         const float* w = wt_all + slot * dk * GC;
         const float* k = kt_all + slot * GC * dk;
-        for (int idx = tid * 4; idx < GC * dk; idx += GC_THREADS * 4) {
+        for (int idx = tid * 4; idx < GC * dk; idx += GS_THREADS * 4) {
             gc_copy16(dst + idx, w + idx);
             gc_copy16(dst + GC * dk + idx, k + idx);
         }
         const int n = min(GC, qlen - c * GC);
         float* up = dst + 2 * GC * dk;
-        for (int idx = tid; idx < GC * (GC_DVS / 4); idx += GC_THREADS) {
+        for (int idx = tid; idx < GC * (GC_DVS / 4); idx += GS_THREADS) {
             const int t = idx / (GC_DVS / 4), c4 = (idx % (GC_DVS / 4)) * 4;
             if (t < n) gc_copy16(up + t * GC_DVS + c4, u_all + (size_t)(c * GC + t) * nH * dv + c4);
             else *reinterpret_cast<float4*>(up + t * GC_DVS + c4) = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -521,7 +528,7 @@ gd_chunk_scan_kernel(const GcParams P) {
         gc_copy_commit();
     };
     fetch(0);
-    const int dkq = dk / 4;                          // a warp's share of the rows of S in U = U' - W S
+    const int dkq = (dk + GS_THREADS / 32 - 1) / (GS_THREADS / 32);     // a warp's share of the rows of S in U = U' - W S
     for (int c = 0; c < nc; ++c) {
         gc_copy_wait();
         __syncthreads();                             // chunk c's tiles and the state's slice are in shared memory
@@ -534,16 +541,15 @@ gd_chunk_scan_kernel(const GcParams P) {
         float* sb = P.sb + slot * dk * dv + v0;
 #pragma unroll
         for (int m = 0; m < NT; ++m) {
-            const int i0 = ((tid + m * GC_THREADS) >> 2) * 4;
+            const int i0 = ((tid + m * GS_THREADS) >> 3) * 4;
 #pragma unroll
             for (int r = 0; r < 4; ++r)
-                if (i0 + r < dk)
-                    *reinterpret_cast<float4*>(sb + (size_t)(i0 + r) * dv + cg4) = make_float4(s[m][r][0], s[m][r][1], s[m][r][2], s[m][r][3]);
+                if (i0 + r < dk) *reinterpret_cast<float2*>(sb + (size_t)(i0 + r) * dv + cg2) = make_float2(s[m][r][0], s[m][r][1]);
         }
         {   // W S: warp w takes rows w*dkq .. of S, lane (t group, column group) a 4 x 4 tile of the product
             const int t0 = (lane >> 2) * 4;
             float acc[4][4] = {};
-            const int i1 = (warp + 1) * dkq;
+            const int i1 = min(dk, (warp + 1) * dkq);
 #pragma unroll 4
             for (int i = warp * dkq; i < i1; ++i) {
                 const float4 w4 = *reinterpret_cast<const float4*>(Wt + i * GC + t0);
@@ -559,52 +565,49 @@ gd_chunk_scan_kernel(const GcParams P) {
             for (int r = 0; r < 4; ++r) *reinterpret_cast<float4*>(dst + r * 4) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
         }
         __syncthreads();
-        {   // U = U' - (the four warps' parts, in ascending order): thread -> token tid / 4, its four columns
-            const int t = tid >> 2;
-            float4 u = *reinterpret_cast<const float4*>(Up + t * GC_DVS + cg4);
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        {   // U = U' - (the warps' parts, in ascending order): thread -> token tid / 8, its two columns
+            const int t = tid >> 3;
+            float2 u = *reinterpret_cast<const float2*>(Up + t * GC_DVS + cg2);
+            float2 a = make_float2(0.f, 0.f);
 #pragma unroll
-            for (int w = 0; w < GC_THREADS / 32; ++w) {
-                const float4 x = *reinterpret_cast<const float4*>(red + (w * 32 + (t >> 2) * 4 + (tid & 3)) * GC_RED + (t & 3) * 4);
-                a.x += x.x, a.y += x.y, a.z += x.z, a.w += x.w;
+            for (int w = 0; w < GS_THREADS / 32; ++w) {
+                const float2 x = *reinterpret_cast<const float2*>(red + (w * 32 + (t >> 2) * 4 + (cg2 >> 2)) * GC_RED + (t & 3) * 4 + (cg2 & 3));
+                a.x += x.x, a.y += x.y;
             }
-            u.x -= a.x, u.y -= a.y, u.z -= a.z, u.w -= a.w;
-            *reinterpret_cast<float4*>(Us + t * GC_DVS + cg4) = u;
-            if (c * GC + t < qlen) *reinterpret_cast<float4*>(u_all + (size_t)(c * GC + t) * nH * dv + cg4) = u;
+            u.x -= a.x, u.y -= a.y;
+            *reinterpret_cast<float2*>(Us + t * GC_DVS + cg2) = u;
+            if (c * GC + t < qlen) *reinterpret_cast<float2*>(u_all + (size_t)(c * GC + t) * nH * dv + cg2) = u;
         }
         __syncthreads();
         const float gam = expf(last);
 #pragma unroll
         for (int m = 0; m < NT; ++m) {
-            const int i0 = ((tid + m * GC_THREADS) >> 2) * 4;
+            const int i0 = ((tid + m * GS_THREADS) >> 3) * 4;
             if (i0 < dk) {
 #pragma unroll
-                for (int r = 0; r < 4; ++r)
-#pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) s[m][r][cc] *= gam;
+                for (int r = 0; r < 4; ++r) s[m][r][0] *= gam, s[m][r][1] *= gam;
 #pragma unroll 4
                 for (int t = 0; t < GC; ++t) {
                     const float4 k4 = *reinterpret_cast<const float4*>(Kt + t * dk + i0);
-                    const float4 u4 = *reinterpret_cast<const float4*>(Us + t * GC_DVS + cg4);
-                    const float kv[4] = {k4.x, k4.y, k4.z, k4.w}, uv[4] = {u4.x, u4.y, u4.z, u4.w};
+                    const float2 u2 = *reinterpret_cast<const float2*>(Us + t * GC_DVS + cg2);
+                    const float kv[4] = {k4.x, k4.y, k4.z, k4.w};
 #pragma unroll
-                    for (int r = 0; r < 4; ++r)
-#pragma unroll
-                        for (int cc = 0; cc < 4; ++cc) s[m][r][cc] = fmaf(kv[r], uv[cc], s[m][r][cc]);
+                    for (int r = 0; r < 4; ++r) {
+                        s[m][r][0] = fmaf(kv[r], u2.x, s[m][r][0]);
+                        s[m][r][1] = fmaf(kv[r], u2.y, s[m][r][1]);
+                    }
                 }
 #pragma unroll
-                for (int r = 0; r < 4; ++r)
-                    *reinterpret_cast<float4*>(Ss + (i0 + r) * GC_DVS + cg4) = make_float4(s[m][r][0], s[m][r][1], s[m][r][2], s[m][r][3]);
+                for (int r = 0; r < 4; ++r) *reinterpret_cast<float2*>(Ss + (i0 + r) * GC_DVS + cg2) = make_float2(s[m][r][0], s[m][r][1]);
             }
         }
     }
 #pragma unroll
     for (int m = 0; m < NT; ++m) {
-        const int i0 = ((tid + m * GC_THREADS) >> 2) * 4;
+        const int i0 = ((tid + m * GS_THREADS) >> 3) * 4;
 #pragma unroll
         for (int r = 0; r < 4; ++r)
-            if (i0 + r < dk)
-                *reinterpret_cast<float4*>(St + (size_t)(i0 + r) * dv + cg4) = make_float4(s[m][r][0], s[m][r][1], s[m][r][2], s[m][r][3]);
+            if (i0 + r < dk) *reinterpret_cast<float2*>(St + (size_t)(i0 + r) * dv + cg2) = make_float2(s[m][r][0], s[m][r][1]);
     }
 }
 
@@ -736,7 +739,7 @@ gd_chunk_out_kernel(const GcParams P) {
 
 static inline size_t gc_prep_smem(int dk, int dv) { return ((size_t)GC * (dk + 1) + GC * GC + 2 * GC + GC * dv) * sizeof(float); }
 static inline size_t gc_scan_smem(int dk) {
-    return ((size_t)2 * (2 * GC * dk + GC * GC_DVS) + dk * GC_DVS + GC * GC_DVS + GC_THREADS * GC_RED) * sizeof(float);
+    return ((size_t)2 * (2 * GC * dk + GC * GC_DVS) + dk * GC_DVS + GC * GC_DVS + GS_THREADS * GC_RED) * sizeof(float);
 }
 static inline size_t gc_out_smem(int dk) { return ((size_t)2 * dk * GC_LDT + GC * GC_LDT + GC) * sizeof(float); }
 
@@ -757,7 +760,7 @@ NG_EXPORT int ng_gated_delta_chunked(const float* conv, const void* p, int ldp, 
                                      int nG, int dk, int dv, int act_bf16, cudaStream_t stream) {
     if (n_entries <= 0 || n_rows <= 0 || max_q <= 0) return NG_OK;
     if (nH <= 0 || nG <= 0 || nH % nG || !ng_gd_chunked_takes(dk, dv) || !scratch || ((uintptr_t)scratch & 15) ||
-        ((uintptr_t)o_raw & 15) || ((uintptr_t)state & 15))
+        ((uintptr_t)o_raw & 15) || ((uintptr_t)state & 15) || ((uintptr_t)conv & 15))
         return NG_BAD_SIZE;
     const size_t n_slots = (size_t)n_rows / GC + n_entries + 1;
     GcParams P;
@@ -787,8 +790,8 @@ NG_EXPORT int ng_gated_delta_chunked(const float* conv, const void* p, int ldp, 
     if (nH > 65535 || n_entries > 65535) return NG_BAD_SIZE;
     if (act_bf16) NG_LAUNCH((gd_chunk_prep_kernel<__nv_bfloat16>), pgrid, GC_THREADS, sp, stream, P);
     else NG_LAUNCH((gd_chunk_prep_kernel<float>), pgrid, GC_THREADS, sp, stream, P);
-    if (dk <= 128) NG_LAUNCH((gd_chunk_scan_kernel<1>), sgrid, GC_THREADS, ss, stream, P);
-    else NG_LAUNCH((gd_chunk_scan_kernel<2>), sgrid, GC_THREADS, ss, stream, P);
+    if (dk <= 128) NG_LAUNCH((gd_chunk_scan_kernel<1>), sgrid, GS_THREADS, ss, stream, P);
+    else NG_LAUNCH((gd_chunk_scan_kernel<2>), sgrid, GS_THREADS, ss, stream, P);
     NG_LAUNCH(gd_chunk_out_kernel, ogrid, GC_THREADS, so, stream, P);
     return ng_launch_status();
 }
