@@ -90,7 +90,7 @@ class GatedDelta:
             need = ops.gated_delta_chunked_scratch(n, ctx.n_entries, s.n_heads, s.key_dim, s.value_dim)
             bound = ops.gated_delta_chunked_scratch(ctx.ws.max_rows, ctx.ws.max_rows // self.CHUNKED_MIN_ROWS + 64,
                                                     s.n_heads, s.key_dim, s.value_dim)
-            chunks = ctx.ws.flat("gd_chunks", need, torch.float32, reserve=max(need, bound))
+            chunks = ctx.ws.flat(f"gd_chunks_{s.n_heads}x{s.key_dim}x{s.value_dim}", need, torch.float32, reserve=max(need, bound))
         ops.gated_delta(p, self.w_conv, self.a_log, self.dt_bias, self.norm, conv_state.state, state.state, conv, o_raw, o,
                         ctx.cu_q, ctx.ctx_before, ctx.slots, ctx.row_entry, ctx.n_entries, ctx.max_q, s.n_heads,
                         s.n_qk_heads, s.key_dim, s.value_dim, s.eps, chunk_scratch=chunks)

@@ -99,7 +99,7 @@ class LatentAttention:
                 n_splits = max(1, min(self.MAX_SPLITS, 128 // n, longest // 64))
             partial = None
             if n_splits > 1:
-                partial = ctx.ws.flat("lat_partial", ops.latent_core_partial_floats(n, H, rp, n_splits), torch.float32,
+                partial = ctx.ws.flat(f"lat_partial_{H}x{rp}", ops.latent_core_partial_floats(n, H, rp, n_splits), torch.float32,
                                       reserve=ops.latent_core_partial_floats(self.SPLIT_MAX_ROWS, H, rp, self.MAX_SPLITS))
             ops.latent_core(q, cache.k_pages, cache.table, ctx.positions, ctx.row_entry, gate, o, H, s.window,
                             s.softmax_scale, n_splits, partial)

@@ -173,7 +173,9 @@ class MappedAttention:
                 ops.mapped_attention_group_takes(s.key_dim, s.value_dim, s.n_heads, s.n_kv_heads, self.dtype):
             n_splits = self._group_splits(n, cache)
             per_run = ops.mapped_attention_partial_floats(1, s.n_heads, s.n_maps, s.value_dim, 2) // 2
-            partial = ctx.ws.flat("mattn_group_partial", n * n_splits * per_run, torch.float32,
+            # (scratch whose bound follows from the layer's sizes is named after them: a layer of other sizes has its own)
+            partial = ctx.ws.flat(f"mattn_group_partial_{s.n_heads}x{s.n_maps}x{s.value_dim}", n * n_splits * per_run,
+                                  torch.float32,
                                   reserve=max(self.GROUP_MAX_RUNS, min(ctx.ws.max_rows, self.GROUP_MAX_ROWS)) * per_run)
             ops.mapped_attention_group(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, ctx.row_entry,
                                        out, partial, ctx.n_entries, s.n_heads, s.n_maps, s.window, s.keep_first,
@@ -190,8 +192,8 @@ class MappedAttention:
         if n_splits > 1 or ctx.ws.fixed:
             bound = ops.mapped_attention_partial_floats(min(ctx.ws.max_rows, self.SPLIT_MAX_ROWS), s.n_heads, s.n_maps,
                                                         s.value_dim, self.MAX_SPLITS)
-            partial = ctx.ws.flat("mattn_partial", ops.mapped_attention_partial_floats(n, s.n_heads, s.n_maps, s.value_dim,
-                                                                                       n_splits), torch.float32, reserve=bound)
+            need = ops.mapped_attention_partial_floats(n, s.n_heads, s.n_maps, s.value_dim, n_splits)
+            partial = ctx.ws.flat(f"mattn_partial_{s.n_heads}x{s.n_maps}x{s.value_dim}", need, torch.float32, reserve=bound)
         ops.mapped_attention(q, cache.k_pages, cache.v_pages, cache.table, ctx.positions, ctx.row_entry, out, s.n_heads,
                              s.n_maps, s.window, s.keep_first, s.softmax_scale, s.softcap or 0.0, self.lam,
                              s.n_maps == 2, 1.0 - s.diff, s.eps, n_splits, partial, **extra)

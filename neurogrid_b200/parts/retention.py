@@ -77,7 +77,7 @@ class Retention:
             need = ops.retention_chunked_scratch(n, ctx.n_entries, s.n_heads, s.key_dim, s.value_dim)
             bound = ops.retention_chunked_scratch(ctx.ws.max_rows, ctx.ws.max_rows // self.CHUNKED_MIN_ROWS + 64,
                                                   s.n_heads, s.key_dim, s.value_dim)
-            states = ctx.ws.flat("ret_states", need, torch.float32, reserve=max(need, bound))
+            states = ctx.ws.flat(f"ret_states_{s.n_heads}x{s.key_dim}x{s.value_dim}", need, torch.float32, reserve=max(need, bound))
         ops.retention(p, pa.inv_freq if rot else None, rot, self.decay, cache.state, o, ctx.cu_q, ctx.ctx_before,
                       ctx.slots, ctx.n_entries, s.n_heads, s.key_dim, s.value_dim, s.eps, scratch=scratch,
                       state_scratch=states, max_q=ctx.max_q)

@@ -80,8 +80,21 @@ FUZE_W = {
     ],
 }
 
-CONFIGS = {"S": (FUZE_S, 31), "U": (FUZE_U, 32), "W": (FUZE_W, 33)}
-PAGE_SIZE = {"S": 8, "U": 16, "W": 8}
+# V: layers whose scratch needs differ: attention without a mask over hundreds of keys (a step of few rows cuts them
+# into runs) with other head counts and value sizes in every layer, recurrent heads of two sizes that both run chunk by
+# chunk; a step's fixed workspace must hold every layer's share
+FUZE_V = {
+    "architecture": "Fuzelorn", "vocab": 120, "width": 48, "norm": {"eps": 1e-5}, "logit_softcap": 20.0,
+    "embedding": {"scale": 1.25, "bigram": {"buckets": 19, "mul_prev": 5, "mul_cur": 2}},
+    "layers": [
+        _layer(_left(2, 1, 16, 16, 0.3, None), _right(2, 1, 16, 16, 3), {"kind": "dense", "ff": 32}),
+        _layer(_left(8, 2, 32, 48, 0.25, None, (0.2, 50)), _right(4, 2, 32, 48, 4), _moe(4, 2, 16, 1.0, (2, 1), (16, 1.5))),
+        _layer(_left(4, 4, 16, 32, 0.3, 150), _right(3, 3, 8, 32, 2), None),
+    ],
+}
+
+CONFIGS = {"S": (FUZE_S, 31), "U": (FUZE_U, 32), "W": (FUZE_W, 33), "V": (FUZE_V, 34)}
+PAGE_SIZE = {"S": 8, "U": 16, "W": 8, "V": 16}
 
 
 def draw_weights(config: dict, seed: int, router_gain: float = 3.0):

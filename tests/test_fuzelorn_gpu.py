@@ -551,7 +551,7 @@ def test_routed_experts_with_clamped_activation_and_gated_shared_expert(dtype, E
 
 
 # ------------------------------------------------------------------------------------------ whole models
-LENS = {"S": [1, 9, 40, 131, 64, 23, 77], "U": [3, 50, 97, 30, 64], "W": [2, 17, 150, 33]}
+LENS = {"S": [1, 9, 40, 131, 64, 23, 77], "U": [3, 50, 97, 30, 64], "W": [2, 17, 150, 33], "V": [200, 2, 100, 70]}
 
 
 def _dir(dirs, name, dtype):
@@ -606,7 +606,7 @@ def test_residual_stream_after_every_layer_run(fuzelorn_dirs):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["S", "U", "W"])
+@pytest.mark.parametrize("name", ["S", "U", "W", "V"])
 @pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
 def test_cuts_against_plain(fuzelorn_dirs, plain_logits, name, dtype, cut):
     key = name if dtype == torch.float32 else name + "_calm"
