@@ -42,6 +42,7 @@ struct GemmParams {
     int w_bytes;               // bytes of W a stage receives (rows, or 2 * rows for SwiGLU, times 128)
     int red_v4;                // EPI_RED: four columns per atomic (N, ldc multiples of 4, out 16-byte aligned)
     int gate_gelu;             // EPI_SWIGLU: the gate's activation is the tanh form of gelu instead of silu
+    int relu2;                 // EPI_BF16: out = relu(y)^2 of the rounded y = x w^T + bias (what a separate pass over y gives)
 };
 
 template <int TN, int EPI>
@@ -254,7 +255,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                             atomicAdd(reinterpret_cast<float*>(p.out) + (size_t)m * p.ldc + n, v[j]);
                         } else {
                             const float b = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
-                            reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v[j] + b);
+                            bf16 y = __float2bfloat16_rn(v[j] + b);
+                            if (p.relu2) {
+                                const float r = fmaxf(__bfloat162float(y), 0.f);
+                                y = __float2bfloat16_rn(r * r);
+                            }
+                            reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = y;
                         }
                     }
                 }
@@ -301,6 +307,7 @@ static int dispatch_tn(int tn, const CUtensorMap& mw, const CUtensorMap& mx, con
 //   epi 2: out bf16 [M, ldc] = silu(x wg^T) * (x wu^T)     wg = w rows [0, N), wu = w rows [up_row_offset, +N)
 //   epi 3: out float [M, ldc] += x w^T (atomic adds; any splits)
 //   epi 4: as epi 2 with gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) for silu
+//   epi 5: as epi 0, then relu(.)^2 of the rounded result
 // tn: token tile (16, 32, 64, 128, 256; 0 = chosen from M).
 NG_EXPORT int ng_gemm_sm100(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
                             int n_w_rows, int ldc, int epi, int splits, int up_row_offset, int tn, int* status,
@@ -308,8 +315,9 @@ NG_EXPORT int ng_gemm_sm100(const void* x, const void* w, const void* bias, void
     if (M <= 0 || N <= 0) return NG_OK;
     if (K <= 0 || K % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ldc < N || splits < 1 || !status)
         return NG_BAD_SIZE;
-    const int gate_gelu = epi == 4;
+    const int gate_gelu = epi == 4, relu2 = epi == 5;
     if (gate_gelu) epi = EPI_SWIGLU;
+    if (relu2) epi = EPI_BF16;
     if (epi < 0 || epi > 3 || ((epi == EPI_BF16 || epi == EPI_SWIGLU) && splits != 1) ||
         (epi == EPI_SWIGLU && up_row_offset + N > n_w_rows))
         return NG_BAD_SIZE;
@@ -324,7 +332,7 @@ NG_EXPORT int ng_gemm_sm100(const void* x, const void* w, const void* bias, void
     if (!tensor_map(w, n_w_rows, K, rows, &mw)) return NG_LAUNCH_FAILED;
     if (!tensor_map(x, M, K, tn, &mx)) return NG_LAUNCH_FAILED;
     const int red_v4 = epi == EPI_RED && N % 4 == 0 && ldc % 4 == 0 && rows % 4 == 0 && ((uintptr_t)out & 15) == 0;
-    GemmParams p{out, (const bf16*)bias, status, M, N, K, ldc, per, up_row_offset, rows, w_bytes, red_v4, gate_gelu};
+    GemmParams p{out, (const bf16*)bias, status, M, N, K, ldc, per, up_row_offset, rows, w_bytes, red_v4, gate_gelu, relu2};
     dim3 grid((N + rows - 1) / rows, (M + tn - 1) / tn, splits);
     if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
     switch (epi) {

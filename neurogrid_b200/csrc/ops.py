@@ -794,6 +794,16 @@ def pair_norm_mean(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch
              int(bool(accumulate)), int(act_dtype == torch.bfloat16), _stream()), "pair_norm_mean")
 
 
+def linear_relu_squared(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out = relu(x @ weight^T + bias)^2: in the product's epilogue where the tcgen05 kernel runs the product (steps of
+    few rows), else the product and one pass over it; both square the same rounded value."""
+    if x.dtype == torch.bfloat16 and x.is_cuda and out.dtype == torch.bfloat16 and gemm_sm100_ok(x, weight):
+        gemm_sm100(x, weight, bias, out, relu_squared=True)
+        return
+    linear(x, weight, bias, out)
+    relu_squared_(out)
+
+
 def relu_squared_(x: torch.Tensor) -> None:
     """x <- relu(x)^2 in place."""
     f = _fn("elementwise", "ng_unary", [_c_void_p, _c_ll, _c_int, _c_float, _c_int, _c_void_p])
@@ -966,13 +976,16 @@ def gemm_sm100_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_sm100(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, *,
-               splits: int = 1, token_tile: int = 0) -> None:
+               splits: int = 1, token_tile: int = 0, relu_squared: bool = False) -> None:
     """out = x @ w^T on tcgen05/TMA.  out bf16 [M,N] (+ bias), or float32 [M,N], or float32
-    [S,M,N] partial sums over S = splits of K (``gemm_splits`` tells S for a K)."""
+    [S,M,N] partial sums over S = splits of K (``gemm_splits`` tells S for a K).  ``relu_squared`` (bf16 out): the
+    epilogue squares what is positive of the rounded result and zeroes the rest, as ``relu_squared_`` over it would."""
     M, K = x.shape
     N = w.shape[0]
+    if relu_squared and out.dtype != torch.bfloat16:
+        raise KernelError("gemm_sm100: the squared relu rides in the bf16 epilogue only")
     if out.dtype == torch.bfloat16:
-        epi, s_eff = 0, 1
+        epi, s_eff = (5 if relu_squared else 0), 1
         if out.shape != (M, N) or splits != 1:
             raise KernelError("gemm_sm100: bf16 output is [M, N] without splits")
     else:

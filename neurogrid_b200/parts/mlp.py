@@ -10,7 +10,8 @@ from .registry import register
 
 @register("ffn", "mlp")
 class MLP:
-    """y = W_down act(W_up x + b_up) + b_down with act the square of relu; the biases ride in the products."""
+    """y = W_down act(W_up x + b_up) + b_down with act the square of relu; the biases ride in the products, and in a
+    step of few rows so does the activation."""
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
 
@@ -41,6 +42,5 @@ class MLP:
     def forward(self, x, ctx):
         s = self.spec
         act = ctx.ws.buf("ffn_act", x.shape[0], s.intermediate, self.dtype)
-        ops.linear(x, self.w_up, self.b_up, act)
-        ops.relu_squared_(act)
+        ops.linear_relu_squared(x, self.w_up, self.b_up, act)
         return ops.linear_to_residual(act, self.w_down, self.b_down, ctx.ws, "ffn_out", residual=ctx.residual)

@@ -476,6 +476,27 @@ def test_feed_forward_with_squared_relu_and_biases(dtype, n):
     assert rel_err(y.sum(0) if y.dim() == 3 else y, want) < TOL[dtype]
 
 
+@pytest.mark.parametrize("n,H,I", [(1, 64, 96), (8, 72, 200), (33, 128, 136), (64, 256, 320)])
+def test_squared_relu_in_the_product_equals_a_pass_over_it(n, H, I):
+    """Few rows: the tensor-core product squares what is positive of its rounded result in the epilogue; the same bits
+    as the product followed by the elementwise kernel, with and without a bias, beside the plain statement."""
+    o = ops()
+    g = torch.Generator().manual_seed(n + I)
+    x = torch.randn(n, H, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(I, H, generator=g) / H ** 0.5).to(torch.bfloat16).to(DEV)
+    for bias in (None, (0.5 * torch.randn(I, generator=g)).to(torch.bfloat16).to(DEV)):
+        assert o.gemm_sm100_ok(x, w)
+        fused = torch.full((n, I), 7.0, dtype=torch.bfloat16, device=DEV)
+        o.linear_relu_squared(x, w, bias, fused)
+        apart = torch.empty_like(fused)
+        o.linear(x, w, bias, apart)
+        o.relu_squared_(apart)
+        assert torch.equal(fused, apart)
+        y = x.double() @ w.double().t() + (0 if bias is None else bias.double())
+        assert rel_err(fused, torch.relu(y) ** 2) < TOL[torch.bfloat16]
+        assert (fused >= 0).all() and (fused == 0).any() and (fused > 0).any()
+
+
 def _route_on_gpu(z, corr, router):
     """The router kernel on logits given outright: the router's matrix is the identity."""
     E = z.shape[1]
