@@ -417,8 +417,9 @@ def test_gated_delta_rule_long_portions_in_chunks():
 # ------------------------------------------------------------------------------------------ the two mixers side by side
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("accumulate", [False, True])
-def test_mean_of_two_normed_inputs(dtype, accumulate):
-    n, H = 9, 300
+@pytest.mark.parametrize("H", [300, 2048, 2500])
+def test_mean_of_two_normed_inputs(dtype, accumulate, H):
+    n = 9
     a, b = _x((n, H), dtype, seed=1, scale=5.0), torch.randn(3, n, H, device=DEV)           # b: a stack of partial sums
     wa, wb = (1 + 0.3 * torch.randn(H)).to(DEV), (1 + 0.3 * torch.randn(H)).to(DEV)
     out = torch.randn(n, H, device=DEV)
