@@ -16,6 +16,7 @@ from .lfm2 import ConfigError, Lfm2Config
 from .metanex import MetanexConfig
 from .rofulorn import RofulornConfig
 from .fuzelorn import FuzelornConfig
+from .dodilix import DodilixConfig
 
 _ARCHITECTURES: Dict[str, Any] = {}
 _MODEL_TYPES: Dict[str, str] = {}
@@ -64,3 +65,4 @@ register_architecture("Lfm2ForCausalLM", Lfm2Config, model_type="lfm2")
 register_architecture("Metanex", MetanexConfig)
 register_architecture("Rofulorn", RofulornConfig)
 register_architecture("Fuzelorn", FuzelornConfig)
+register_architecture("Dodilix", DodilixConfig)

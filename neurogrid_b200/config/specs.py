@@ -135,6 +135,11 @@ class MappedAttentionSpec:
     multiplied by 1 + c ln(floor((p + 1) / m) + 1) at position p (c = 0: not).  ``sink``: a learned number per head
     whose exponential is one more term of the softmax's denominator; it has no key and no value, is not scaled and
     gets no bias.  A ``position`` with score slopes takes slope_h (i - j) off the scaled (and capped) score.
+    ``chunk`` c: a query also sees only the keys of its own chunk, floor(j / c) = floor(i / c), chunks counted from the
+    sequence's position 0 (``cache_window`` is then c: no later query reads further back).  ``norm_weight`` False: the
+    RMS norm of q and k has no weights, and since a rotation keeps a head's sum of squares it may be taken on either
+    side of ``position``.  ``out_gate``: the concatenated heads are multiplied element by element by the sigmoid of
+    one more projection of the mixer's input (rows ``g``) before the output projection.
     """
     hidden: int
     n_heads: int
@@ -157,9 +162,12 @@ class MappedAttentionSpec:
     q_temp_coef: float = 0.0
     q_temp_every: int = 1
     sink: bool = False
+    chunk: Optional[int] = None
+    norm_weight: bool = True
+    out_gate: bool = False
     names: Mapping[str, str] = field(default_factory=lambda: _names(
         q="q", k="k", v="v", o="o", q_bias="q.b", k_bias="k.b", v_bias="v.b", o_bias="o.b", q_norm="q.norm",
-        k_norm="k.norm", lq1="lq1", lk1="lk1", lq2="lq2", lk2="lk2", sink="sink"))
+        k_norm="k.norm", lq1="lq1", lk1="lk1", lq2="lq2", lk2="lk2", sink="sink", out_gate="g"))
     kind: str = "mapped_attention"
 
     def __post_init__(self):
@@ -175,6 +183,10 @@ class MappedAttentionSpec:
             raise ValueError("keep_first must be >= 0 and softcap positive")
         if self.norm_scope not in ("head", "projection") or self.q_temp_every < 1:
             raise ValueError("norm_scope is 'head' or 'projection', q_temp_every at least 1")
+        if self.chunk is not None and (self.chunk < 1 or self.window is not None or self.keep_first):
+            raise ValueError("a chunked mask has a positive size and goes without a window or kept first tokens")
+        if not self.norm_weight and self.norm_scope != "head":
+            raise ValueError("a norm without weights is a norm per head")
 
 
 @dataclass(frozen=True)
@@ -251,6 +263,10 @@ class LatentAttentionSpec:
     head k = W_uk c and v = W_uv c; only c is cached.  ``window`` None = every earlier key, W = the last W
     keys with the query's own.  Head h's output is multiplied by sigmoid(W_g x)_h before the output
     projection.  Both norms have plain weights and ``eps``.
+    ``rope_dim`` r > 0: q has r more coordinates per head (laid out [key_dim | r]) and W_dkv r more rows, one key
+    part shared by all heads and not normed; both are rotated by ``position`` (over all r coordinates) and the score
+    is the sum of the two dot products.  The latent and the rotated key part are cached.  ``gate`` "element": the
+    gate has a row per coordinate of the concatenated heads instead of one per head.
     """
     hidden: int
     n_heads: int
@@ -261,6 +277,9 @@ class LatentAttentionSpec:
     softmax_scale: float
     eps: float
     window: Optional[int] = None
+    rope_dim: int = 0
+    position: object = None
+    gate: str = "head"
     names: Mapping[str, str] = field(default_factory=lambda: _names(
         dq="dq", dq_norm="dq.norm", uq="uq", dkv="dkv", dkv_norm="dkv.norm", uk="uk", uv="uv", gate="g", o="o"))
     kind: str = "latent_attention"
@@ -270,6 +289,10 @@ class LatentAttentionSpec:
             raise ValueError("attention window must be >= 1")
         if not (1 <= self.kv_rank <= 512):
             raise ValueError(f"latent attention: kv_rank must be in [1, 512], got {self.kv_rank}")
+        if self.rope_dim < 0 or self.rope_dim % 2 or (self.rope_dim > 0) != (self.position is not None):
+            raise ValueError("latent attention: a rotated key part has an even size and a position encoding")
+        if self.gate not in ("head", "element"):
+            raise ValueError("latent attention: the gate is per head or per element")
 
 
 @dataclass(frozen=True)
@@ -284,7 +307,10 @@ class MoESpec:
     be chosen), and weighted by s over the sum of the chosen s (+ 1e-20).
     ``activation`` "swiglu": silu(gate) * up.  "clamped_glu": g = min(gate, limit), u = clamp(up, -limit, limit),
     g sigmoid(``glu_alpha`` g) (u + 1); the shared expert has a ``shared_limit`` of its own.
-    ``shared_gate``: the shared expert's output is multiplied by sigmoid(w . x), one number per token."""
+    ``shared_gate``: the shared expert's output is multiplied by sigmoid(w . x), one number per token.
+    ``scoring`` "softmax_all": scores s = softmax(logits) over ALL experts, no bias, and then as for sigmoid scores
+    (correction, groups, s over the chosen sum).  ``group_score`` "top2" (the sum of a group's two largest choice
+    scores) or "max".  ``route_scale`` multiplies the routing weights."""
     hidden: int
     n_experts: int
     top_k: int
@@ -299,6 +325,8 @@ class MoESpec:
     shared_limit: float = 0.0
     glu_alpha: float = 1.702
     shared_gate: bool = False
+    group_score: str = "top2"
+    route_scale: float = 1.0
     names: Mapping[str, str] = field(default_factory=lambda: _names(
         expert="e{}", gate="gate", up="up", down="down", router="router", router_bias="router.b", shared="shared",
         correction="correction", shared_gate="shared.sg"))
@@ -309,8 +337,12 @@ class MoESpec:
             raise ValueError(f"moe: top_k {self.top_k} must be in 1..{self.n_experts}")
         if self.top_k > 32:
             raise ValueError("moe: top_k above 32 is not supported")
-        if self.scoring not in ("softmax", "sigmoid") or self.activation not in ("swiglu", "clamped_glu"):
-            raise ValueError("moe: scoring is softmax or sigmoid, activation swiglu or clamped_glu")
+        if self.scoring not in ("softmax", "sigmoid", "softmax_all") or self.activation not in ("swiglu", "clamped_glu"):
+            raise ValueError("moe: scoring is softmax, sigmoid or softmax_all, activation swiglu or clamped_glu")
+        if self.group_score not in ("top2", "max"):
+            raise ValueError("moe: a group's score is top2 or max")
+        if self.scoring == "softmax" and self.route_scale != 1.0:
+            raise ValueError("moe: a scale of the routing weights goes with sigmoid or softmax_all scoring")
         if self.n_groups < 1 or self.n_experts % self.n_groups or not (1 <= self.keep_groups <= self.n_groups):
             raise ValueError(f"moe: {self.n_experts} experts do not form {self.n_groups} equal groups of which {self.keep_groups} are kept")
         if self.top_k > self.keep_groups * (self.n_experts // self.n_groups):
@@ -319,8 +351,8 @@ class MoESpec:
             raise ValueError("moe: a correction and groups go with sigmoid scoring")
         if self.activation == "clamped_glu" and not (self.limit > 0 and (self.shared_ff == 0 or self.shared_limit > 0)):
             raise ValueError("moe: the clamped activation needs positive limits")
-        if self.shared_gate and not (self.shared_ff and self.scoring == "sigmoid" and self.activation == "clamped_glu"):
-            raise ValueError("moe: a gate of the shared expert needs a shared expert, sigmoid scoring and the clamped activation")
+        if self.shared_gate and not (self.shared_ff and self.scoring != "softmax"):
+            raise ValueError("moe: a gate of the shared expert needs a shared expert and sigmoid or softmax_all scoring")
 
 
 @dataclass(frozen=True)
@@ -376,14 +408,48 @@ class GatedDeltaSpec:
 @dataclass(frozen=True)
 class SideBySideSpec:
     """Two mixers that read the same input; the result is half the sum of their outputs, each first divided by its
-    root mean square over the model width (``eps``) and multiplied by a plain weight of its own."""
+    root mean square over the model width (``eps``) and multiplied by a plain weight of its own.
+    ``combine`` "weighted": the result is left_scale * left + right_scale * right instead (no norms, no weights)."""
     hidden: int
     left: object
     right: object
     eps: float
+    combine: str = "norm_mean"
+    left_scale: float = 1.0
+    right_scale: float = 1.0
     names: Mapping[str, str] = field(default_factory=lambda: _names(left="left", right="right", left_out="left.out",
                                                                    right_out="right.out"))
     kind: str = "side_by_side"
+
+    def __post_init__(self):
+        if self.combine not in ("norm_mean", "weighted"):
+            raise ValueError("side by side: combine is norm_mean or weighted")
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec:
+    """Linear attention whose state decays per key channel and token:
+
+        S <- diag(alpha_t) S + k_t v_t^T;   o_t = S^T q_t       (S [key_dim, value_dim] per head, float32, zero at the start)
+
+    q = W_q x * key_dim^(-1/2), k = W_k x (``n_heads`` heads of ``key_dim``), v = W_v x (heads of ``value_dim``);
+    alpha = sigmoid(z)^(1/tau) with z = W_a2 (W_a1 x) + b, laid out heads x key_dim, through a low-rank pair of
+    matrices (``decay_rank`` columns between them).  Each head's o is RMS-normed over value_dim with a plain weight
+    shared by the heads (``eps``), the heads are multiplied by silu(W_g x) and projected back."""
+    hidden: int
+    n_heads: int
+    key_dim: int
+    value_dim: int
+    decay_rank: int
+    tau: float
+    eps: float
+    names: Mapping[str, str] = field(default_factory=lambda: _names(
+        q="q", k="k", v="v", gate="g", o="o", norm="norm", decay_down="a1", decay_up="a2", decay_bias="a2.b"))
+    kind: str = "gated_linear_attention"
+
+    def __post_init__(self):
+        if min(self.n_heads, self.key_dim, self.value_dim, self.decay_rank) < 1 or not self.tau > 0:
+            raise ValueError("gated linear attention: heads, sizes and tau must be positive")
 
 
 @dataclass(frozen=True)
@@ -479,11 +545,17 @@ class ModelSpec:
                                                  # token embeddings (no LFM2 configuration has one)
     token_pair: Optional[object] = None          # a TokenPairSpec: an embedding of (previous token, token), added too
     logit_softcap: Optional[float] = None        # logits <- cap * tanh(logits / cap)
+    logit_scale: float = 1.0                     # logits <- logits * scale
+    streams: int = 0                             # > 0: the residual stream is that many copies (hyper-connections); every
+                                                 # layer's block arrangement then keeps them ("hyper")
 
     def __post_init__(self):
         n = len(self.layers)
         if self.position_table_name and self.max_positions <= 0:
             raise ValueError("a table of learned positions needs max_positions")
+        if self.streams < 0 or (self.streams > 0) != any(l.block == "hyper" for l in self.layers) \
+                or (self.streams > 0 and not all(l.block == "hyper" for l in self.layers)):
+            raise ValueError("a model with several copies of the stream has hyper blocks in every layer, and only such a model")
         writers = set()
         for e in self.schedule:
             if not (0 <= e.layer < n) or e.cache < 0:

@@ -37,6 +37,7 @@ SOURCES: Dict[str, Sequence[str]] = {
     "attention_sm100": (),
     "input_conv": (), "retention": (), "latent": (), "latent_mma": (), "moe": (), "token_side": (),
     "mapped_attention": (), "mapped_attention_mma": (), "gated_delta": (),
+    "hyper": (), "gated_linear": (),
 }
 
 _lock = threading.RLock()

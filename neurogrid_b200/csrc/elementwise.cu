@@ -456,7 +456,8 @@ NG_EXPORT int ng_pair_norm_mean(const void* a, int a_f32, int a_parts, long long
 }
 
 // ---------------------------------------------------------------------------------- small in-place maps
-// kind 0: x <- relu(x)^2 (over [n] elements of the activation type);  kind 1: x <- cap * tanh(x / cap) (float32)
+// kind 0: x <- relu(x)^2 (over [n] elements of the activation type);  kind 1: x <- cap * tanh(x / cap) (float32);
+// kind 2: x <- x * param
 template <typename T>
 __global__ void unary_kernel(T* __restrict__ x, size_t n, int kind, float param) {
     ng_pdl_trigger();
@@ -466,16 +467,46 @@ __global__ void unary_kernel(T* __restrict__ x, size_t n, int kind, float param)
     const float v = ng_ld(x + i);
     float y;
     if (kind == 0) { const float r = fmaxf(v, 0.f); y = r * r; }
+    else if (kind == 2) y = v * param;
     else y = param * tanhf(v / param);
     ng_st(x + i, y);
 }
 
 NG_EXPORT int ng_unary(void* x, long long n, int kind, float param, int x_bf16, cudaStream_t stream) {
     if (n <= 0) return NG_OK;
-    if (kind < 0 || kind > 1 || (kind == 1 && !(param > 0.f))) return NG_BAD_SIZE;
+    if (kind < 0 || kind > 2 || (kind == 1 && !(param > 0.f))) return NG_BAD_SIZE;
     const long long blocks = (n + 255) / 256;
     if (blocks > 0x7fffffffLL) return NG_BAD_SIZE;
     if (x_bf16) NG_LAUNCH((unary_kernel<__nv_bfloat16>), (unsigned)blocks, 256, 0, stream, (__nv_bfloat16*)x, (size_t)n, kind, param);
     else NG_LAUNCH((unary_kernel<float>), (unsigned)blocks, 256, 0, stream, (float*)x, (size_t)n, kind, param);
+    return ng_launch_status();
+}
+
+// ---------------------------------------------------------------------------------- an output gate, element by element
+// y[row, j] = y[row, j] * act(g[row, j]) * scale over [n_rows, I]; act 0: none (g unused), 1: sigmoid, 2: silu; float32
+// math, one rounding.  Rows of y lie `ldy` elements apart and rows of g `ldg` (blocks of columns of wider buffers).
+template <typename T>
+__global__ void gate_mul_kernel(T* __restrict__ y, const T* __restrict__ g, int I, int ldy, int ldg, int act, float scale) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const size_t row = blockIdx.x;
+    const int j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j >= I) return;
+    float f = scale;
+    if (act) {
+        const float z = ng_ld(g + row * (size_t)ldg + j);
+        const float s = 1.f / (1.f + expf(-z));
+        f *= act == 1 ? s : z * s;
+    }
+    ng_st(y + row * (size_t)ldy + j, ng_ld(y + row * (size_t)ldy + j) * f);
+}
+
+NG_EXPORT int ng_gate_mul(void* y, const void* g, int n_rows, int I, int ldy, int ldg, int act, float scale, int act_bf16,
+                          cudaStream_t stream) {
+    if (n_rows <= 0) return NG_OK;
+    if (I <= 0 || (I + 255) / 256 > 65535 || ldy < I || act < 0 || act > 2 || (act && (!g || ldg < I))) return NG_BAD_SIZE;
+    dim3 grid(n_rows, (I + 255) / 256);
+    if (act_bf16) NG_LAUNCH((gate_mul_kernel<__nv_bfloat16>), grid, 256, 0, stream, (__nv_bfloat16*)y, (const __nv_bfloat16*)g, I, ldy, ldg, act, scale);
+    else NG_LAUNCH((gate_mul_kernel<float>), grid, 256, 0, stream, (float*)y, (const float*)g, I, ldy, ldg, act, scale);
     return ng_launch_status();
 }

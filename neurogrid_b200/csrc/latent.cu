@@ -1,11 +1,20 @@
 // Latent attention, the row kernels around its attention core.
 //
-// latent_prep: a row of the stacked down projection is [c_q raw (rq) | c raw (rkv) | gate logits (nH)].
+// latent_prep: a row of the stacked down projection is [c_q raw (rq) | c raw (rkv) | key part raw (rot) | gate logits (nH)].
 //   c_q = c_q raw / sqrt(mean(c_q raw^2) + eps) * wq        -> cq_out [n_rows, rq]      (activation type)
 //   c   = c raw   / sqrt(mean(c raw^2) + eps) * wkv         -> the row's place in the layer's pages
-//                                                             [pages, 1, page_size, rp], columns rkv..rp zero
-//   gate = sigmoid(gate logits)                             -> gate_out [n_rows, nH]    (float32)
-// Both norms and the gate are float32; only what a matrix product or the cache reads is rounded.
+//                                                             [pages, 1, page_size, rp], columns rkv+rot..rp zero
+//   key part (rot columns, not normed), rotated by the row's position: pair i is (2i, 2i+1) or, with half
+//   pairing, (i, i + rot/2), its angle position * inv_freq[i]  -> columns rkv..rkv+rot of the same place
+//   gate = sigmoid(gate logits)                             -> gate_out [n_rows, nH]    (float32; nH: gate columns)
+// rkv = 0 (no pages): a layer that reads another layer's latents.
+// Both norms, the angles and the gate are float32; only what a matrix product or the cache reads is rounded.
+//
+// latent_rope_q: columns off..off+rot of every head of q [n_rows, nH * rp] are rotated in place the same way.
+//
+// head_up_gate: out[row, h, :] = (W[h] o[row, h, :rank]) * gate[row, h, :] for W [nH, dv, rank]: what a head's
+//   weighted latents become when the expansion to values cannot be folded into the output projection (a gate per
+//   element sits between them).
 //
 // head_gate: y[row, h, :] *= gate[row, h] for rows of [n_rows, nH * width] (for a core that does not gate itself).
 #include "ng_common.cuh"
@@ -16,14 +25,14 @@ latent_prep_kernel(const T* __restrict__ x, const float* __restrict__ wq, const 
                    T* __restrict__ cq_out, T* __restrict__ pages, float* __restrict__ gate_out,
                    const int* __restrict__ table, int table_stride, const int* __restrict__ positions,
                    const int* __restrict__ row_entry, int rq, int rkv, int rp, int nH, int page_size, int num_pages,
-                   float eps, int* __restrict__ status) {
+                   float eps, int* __restrict__ status, int rot, const float* __restrict__ inv_freq, int half_pairing) {
     __shared__ float red[32];
     ng_pdl_trigger();
     ng_pdl_wait();
     const int row = blockIdx.x;
     const int entry = row_entry[row];
     if (entry < 0) return;
-    const T* xr = x + (size_t)row * (rq + rkv + nH);
+    const T* xr = x + (size_t)row * (rq + rkv + rot + nH);
     float ss = 0.f;
     for (int i = threadIdx.x; i < rq; i += blockDim.x) {
         const float v = ng_ld(xr + i);
@@ -32,24 +41,100 @@ latent_prep_kernel(const T* __restrict__ x, const float* __restrict__ wq, const 
     ss = ng_block_sum(ss, red);
     const float r1 = rsqrtf(ss / (float)rq + eps);
     for (int i = threadIdx.x; i < rq; i += blockDim.x) ng_st(cq_out + (size_t)row * rq + i, ng_ld(xr + i) * r1 * wq[i]);
-    ss = 0.f;
-    for (int i = threadIdx.x; i < rkv; i += blockDim.x) {
-        const float v = ng_ld(xr + rq + i);
-        ss += v * v;
-    }
-    ss = ng_block_sum(ss, red);
-    const float r2 = rsqrtf(ss / (float)rkv + eps);
-    const int pos = positions[row];
-    const int page = pos >= 0 ? table[(size_t)entry * table_stride + pos / page_size] : -1;
-    if (page < 0 || page >= num_pages) {
-        if (threadIdx.x == 0) atomicOr(status, NG_STATUS_BAD_PAGE);
-    } else {
-        T* dst = pages + ((size_t)page * page_size + (pos % page_size)) * rp;
-        for (int i = threadIdx.x; i < rp; i += blockDim.x)
-            ng_st(dst + i, i < rkv ? ng_ld(xr + rq + i) * r2 * wkv[i] : 0.f);
+    if (rkv > 0) {
+        ss = 0.f;
+        for (int i = threadIdx.x; i < rkv; i += blockDim.x) {
+            const float v = ng_ld(xr + rq + i);
+            ss += v * v;
+        }
+        ss = ng_block_sum(ss, red);
+        const float r2 = rsqrtf(ss / (float)rkv + eps);
+        const int pos = positions[row];
+        const int page = pos >= 0 ? table[(size_t)entry * table_stride + pos / page_size] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicOr(status, NG_STATUS_BAD_PAGE);
+        } else {
+            T* dst = pages + ((size_t)page * page_size + (pos % page_size)) * rp;
+            for (int i = threadIdx.x; i < rp; i += blockDim.x)
+                if (i < rkv || i >= rkv + rot) ng_st(dst + i, i < rkv ? ng_ld(xr + rq + i) * r2 * wkv[i] : 0.f);
+            const T* kr = xr + rq + rkv;
+            for (int i = threadIdx.x; i < rot / 2; i += blockDim.x) {
+                const int c1 = half_pairing ? i : 2 * i, c2 = half_pairing ? i + rot / 2 : 2 * i + 1;
+                float sn, cs;
+                sincosf((float)pos * inv_freq[i], &sn, &cs);
+                const float a = ng_ld(kr + c1), b = ng_ld(kr + c2);
+                ng_st(dst + rkv + c1, a * cs - b * sn);
+                ng_st(dst + rkv + c2, b * cs + a * sn);
+            }
+        }
     }
     for (int h = threadIdx.x; h < nH; h += blockDim.x)
-        gate_out[(size_t)row * nH + h] = 1.f / (1.f + expf(-ng_ld(xr + rq + rkv + h)));
+        gate_out[(size_t)row * nH + h] = 1.f / (1.f + expf(-ng_ld(xr + rq + rkv + rot + h)));
+}
+
+template <typename T>
+__global__ void latent_rope_q_kernel(T* __restrict__ q, const int* __restrict__ positions, const int* __restrict__ row_entry,
+                                     const float* __restrict__ inv_freq, int nH, int rp, int off, int rot, int half_pairing) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int row = blockIdx.x;
+    if (row_entry[row] < 0) return;
+    const float pos = (float)positions[row];
+    T* qr = q + (size_t)row * nH * rp;
+    const int half = rot / 2;
+    for (int idx = threadIdx.x; idx < nH * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx - h * half;
+        const int c1 = half_pairing ? i : 2 * i, c2 = half_pairing ? i + half : 2 * i + 1;
+        T* p = qr + (size_t)h * rp + off;
+        float sn, cs;
+        sincosf(pos * inv_freq[i], &sn, &cs);
+        const float a = ng_ld(p + c1), b = ng_ld(p + c2);
+        ng_st(p + c1, a * cs - b * sn);
+        ng_st(p + c2, b * cs + a * sn);
+    }
+}
+
+// A block takes HU_ROWS rows of one head: their weighted latents lie in shared memory (float32), a warp takes output
+// columns in turn with its lanes dealt over the latent's coordinates, so W[h] is read once per HU_ROWS rows, in order.
+// A (row, column) sum is formed the same way whatever else the step holds.
+#define HU_ROWS 16
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_up_gate_kernel(const T* __restrict__ o, const T* __restrict__ w, const float* __restrict__ gate, T* __restrict__ out,
+                    int n_rows, int nH, int rp, int rank, int dv, int ldo) {
+    extern __shared__ float os[];                     // [HU_ROWS][rank]
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int r0 = blockIdx.x * HU_ROWS, head = blockIdx.y;
+    const int rows = min(HU_ROWS, n_rows - r0);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    for (int idx = threadIdx.x; idx < HU_ROWS * rank; idx += blockDim.x) {
+        const int r = idx / rank, c = idx - r * rank;
+        os[idx] = r < rows ? ng_ld(o + ((size_t)(r0 + r) * nH + head) * rp + c) : 0.f;
+    }
+    __syncthreads();
+    const T* wh = w + (size_t)head * dv * rank;
+    for (int v = warp; v < dv; v += nwarp) {
+        float acc[HU_ROWS];
+#pragma unroll
+        for (int r = 0; r < HU_ROWS; ++r) acc[r] = 0.f;
+        for (int c = lane; c < rank; c += 32) {
+            const float wv = ng_ld(wh + (size_t)v * rank + c);
+#pragma unroll
+            for (int r = 0; r < HU_ROWS; ++r) acc[r] = fmaf(wv, os[r * rank + c], acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < HU_ROWS; ++r) acc[r] = ng_warp_sum(acc[r]);
+        if (lane < rows) {
+            float y = 0.f;
+#pragma unroll
+            for (int r = 0; r < HU_ROWS; ++r)
+                if (r == lane) y = acc[r];
+            const size_t col = (size_t)head * dv + v;
+            if (gate) y *= gate[(size_t)(r0 + lane) * nH * dv + col];
+            ng_st(out + (size_t)(r0 + lane) * ldo + col, y);
+        }
+    }
 }
 
 template <typename T>
@@ -295,17 +380,58 @@ NG_EXPORT int ng_latent_core(const void* q, const void* pages, const int* table,
 NG_EXPORT int ng_latent_prep(const void* x, const float* wq, const float* wkv, void* cq_out, void* pages,
                              float* gate_out, const int* table, int table_stride, const int* positions,
                              const int* row_entry, int n_rows, int rq, int rkv, int rp, int nH, int page_size,
-                             int num_pages, float eps, int* status, int act_bf16, cudaStream_t stream) {
+                             int num_pages, float eps, int* status, int rot, const float* inv_freq, int half_pairing,
+                             int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
-    if (rq <= 0 || rkv <= 0 || rp < rkv || nH <= 0 || page_size <= 0) return NG_BAD_SIZE;
+    if (rq <= 0 || rkv < 0 || rot < 0 || (rot & 1) || (rot && !inv_freq) || (rkv == 0 && rot) || rp < rkv + rot || nH <= 0 ||
+        page_size <= 0 || (rkv > 0 && !pages))
+        return NG_BAD_SIZE;
     if (act_bf16)
         NG_LAUNCH((latent_prep_kernel<__nv_bfloat16>), n_rows, 128, 0, stream, (const __nv_bfloat16*)x, wq, wkv,
                   (__nv_bfloat16*)cq_out, (__nv_bfloat16*)pages, gate_out, table, table_stride, positions, row_entry,
-                  rq, rkv, rp, nH, page_size, num_pages, eps, status);
+                  rq, rkv, rp, nH, page_size, num_pages, eps, status, rot, inv_freq, half_pairing);
     else
         NG_LAUNCH((latent_prep_kernel<float>), n_rows, 128, 0, stream, (const float*)x, wq, wkv, (float*)cq_out,
                   (float*)pages, gate_out, table, table_stride, positions, row_entry, rq, rkv, rp, nH, page_size,
-                  num_pages, eps, status);
+                  num_pages, eps, status, rot, inv_freq, half_pairing);
+    return ng_launch_status();
+}
+
+NG_EXPORT int ng_latent_rope_q(void* q, const int* positions, const int* row_entry, const float* inv_freq, int n_rows,
+                               int nH, int rp, int off, int rot, int half_pairing, int act_bf16, cudaStream_t stream) {
+    if (n_rows <= 0 || rot == 0) return NG_OK;
+    if (nH <= 0 || rp <= 0 || off < 0 || rot < 0 || (rot & 1) || off + rot > rp || !inv_freq) return NG_BAD_SIZE;
+    if (act_bf16)
+        NG_LAUNCH((latent_rope_q_kernel<__nv_bfloat16>), n_rows, 128, 0, stream, (__nv_bfloat16*)q, positions, row_entry,
+                  inv_freq, nH, rp, off, rot, half_pairing);
+    else
+        NG_LAUNCH((latent_rope_q_kernel<float>), n_rows, 128, 0, stream, (float*)q, positions, row_entry, inv_freq, nH, rp,
+                  off, rot, half_pairing);
+    return ng_launch_status();
+}
+
+// o [n_rows, nH * rp] (the first `rank` columns of a head are read), w [nH, dv, rank], gate float32 [n_rows, nH * dv] or
+// null, out rows `ldo` elements apart (a block of columns of a wider buffer).
+NG_EXPORT int ng_head_up_gate(const void* o, const void* w, const float* gate, void* out, int n_rows, int nH, int rp,
+                              int rank, int dv, int ldo, int act_bf16, cudaStream_t stream) {
+    if (n_rows <= 0) return NG_OK;
+    if (nH <= 0 || nH > 65535 || rank <= 0 || rank > rp || dv <= 0 || ldo < nH * dv) return NG_BAD_SIZE;
+    const size_t smem = (size_t)HU_ROWS * rank * sizeof(float);
+    if (smem > 160 * 1024) return NG_BAD_SIZE;
+    dim3 grid((n_rows + HU_ROWS - 1) / HU_ROWS, nH);
+#define HU_LAUNCH(TT)                                                                                                  \
+    {                                                                                                                  \
+        static bool configured = false;                                                                                \
+        if (!configured) {                                                                                             \
+            if (cudaFuncSetAttribute(head_up_gate_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) \
+                != cudaSuccess)                                                                                        \
+                return NG_LAUNCH_FAILED;                                                                               \
+            configured = true;                                                                                         \
+        }                                                                                                              \
+        NG_LAUNCH((head_up_gate_kernel<TT>), grid, 256, smem, stream, (const TT*)o, (const TT*)w, gate, (TT*)out,      \
+                  n_rows, nH, rp, rank, dv, ldo);                                                                      \
+    }
+    if (act_bf16) HU_LAUNCH(__nv_bfloat16) else HU_LAUNCH(float)
     return ng_launch_status();
 }
 

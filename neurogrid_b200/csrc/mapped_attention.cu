@@ -5,7 +5,7 @@
 //   keys  [pages, nG * M, page, d] values [pages, nG, page, dv]        query head h reads group h / (nH / nG)
 //   s_m(j) = cap(scale * q_m . k_m,j)        cap(s) = softcap * tanh(s / softcap), or s when softcap == 0
 //   a_m    = softmax_j(s_m) v_j  over the visible j: j <= pos and (pos - j < window or j < keep_first);
-//            window 0 = every j <= pos
+//            window 0 = every j <= pos; with `chunk` > 0 also floor(j / chunk) = floor(pos / chunk)
 //   M == 1: o = a_0                          M == 2: o = a_0 - lambda * a_1
 //   slopes (per head, optional): slope_h * (pos - j) is taken off s(j) after the cap
 //   sinks (per head, optional): the softmax's denominator also holds exp(sink_h), a term without key or value
@@ -35,7 +35,7 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
                 T* __restrict__ k_pages, T* __restrict__ v_pages, const int* __restrict__ table, int table_stride,
                 const int* __restrict__ positions, const int* __restrict__ row_entry, int nQ, int nK, int nV, int d,
                 int dv, int page_size, int num_pages, float eps, int* __restrict__ status, int whole, float temp_coef,
-                int temp_every) {
+                int temp_every, int ld, int half_pairing, int unit_norm) {
     extern __shared__ float rot[];                      // cos[rot_dims/2], sin[rot_dims/2]
     __shared__ float red[32];
     ng_pdl_trigger();
@@ -53,8 +53,7 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
     __syncthreads();
     ng_pdl_wait();
     qkv = ng_after_wait(qkv);
-    const int ld = (nQ + nK) * d + nV * dv;
-    const T* in = qkv + (size_t)row * ld;
+    const T* in = qkv + (size_t)row * ld;             // ld: a row's pitch (columns behind v belong to the caller)
     T* qo = q_out + (size_t)row * nQ * d;
     if (entry < 0) {                                   // padding row: defined output, no cache write
         for (int j = blockIdx.y * MA_THREADS + threadIdx.x; j < nQ * d; j += MA_THREADS * gridDim.y) ng_st(qo + j, 0.f);
@@ -98,8 +97,10 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
             const int i = lane + 32 * u;
             x1[u] = x2[u] = 0.f;
             if (i < half) {
-                x1[u] = ng_ld(src + 2 * i);
-                x2[u] = ng_ld(src + 2 * i + 1);
+                // pair i: (2i, 2i+1), or with half pairing (i, i + rot_dims/2) inside the rotated coordinates
+                const bool hp = half_pairing && i < half_rot;
+                x1[u] = ng_ld(src + (hp ? i : 2 * i));
+                x2[u] = ng_ld(src + (hp ? i + half_rot : 2 * i + 1));
             }
             ss += x1[u] * x1[u] + x2[u] * x2[u];
         }
@@ -109,26 +110,33 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
         }
         float r = 1.f;
         if (w) r = whole ? (is_q ? r_q : r_k) : rsqrtf(ng_warp_sum(ss) / (float)d + eps);
+        // a norm without weights: a rotation does not change a head's sum of squares, so the factor of the
+        // unrotated head is the factor of the rotated one
+        else if (unit_norm) r = rsqrtf(ng_warp_sum(ss) / (float)d + eps);
         T* dst = is_q ? qo + (size_t)hh * d : k_pages + k_base + (size_t)(hh - nQ) * page_size * d;
 #pragma unroll
         for (int u = 0; u < MA_MAX_PAIRS; ++u) {
             const int i = lane + 32 * u;
             if (i < half) {
+                const bool hp = half_pairing && i < half_rot;
+                const int c1 = hp ? i : 2 * i, c2 = hp ? i + half_rot : 2 * i + 1;
                 float y1 = x1[u], y2 = x2[u];
-                if (w) { y1 = y1 * r * w[2 * i]; y2 = y2 * r * w[2 * i + 1]; }
+                if (w) { y1 = y1 * r * w[c1]; y2 = y2 * r * w[c2]; }
+                else if (unit_norm) { y1 *= r; y2 *= r; }
                 y1 *= post; y2 *= post;
                 if (i < half_rot) {
                     const float c = rot[i], s = rot[half_rot + i];
                     const float z1 = y1 * c - y2 * s, z2 = y2 * c + y1 * s;
                     y1 = z1; y2 = z2;
                 }
-                ng_st(dst + 2 * i, y1);
-                ng_st(dst + 2 * i + 1, y2);
+                ng_st(dst + c1, y1);
+                ng_st(dst + c2, y2);
             }
         }
         if ((d & 1) && lane == 0) {
             float t = ng_ld(src + d - 1);
             if (w) t = t * r * w[d - 1];
+            else if (unit_norm) t *= r;
             ng_st(dst + d - 1, t * post);
         }
     }
@@ -145,9 +153,10 @@ NG_EXPORT int ng_qkv_prep(const void* qkv, void* q_out, const float* qw, const f
                           int rot_dims, void* k_pages, void* v_pages, const int* table, int table_stride,
                           const int* positions, const int* row_entry, int n_rows, int nQ, int nK, int nV, int d, int dv,
                           int page_size, int num_pages, float eps, int* status, int whole, float temp_coef, int temp_every,
-                          int act_bf16, cudaStream_t stream) {
+                          int ld, int half_pairing, int unit_norm, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (temp_every < 1 || (whole && (!qw || (nK > 0 && !kw)))) return NG_BAD_SIZE;
+    if (ld < (nQ + nK) * d + nV * dv || (unit_norm && (whole || qw || kw))) return NG_BAD_SIZE;
     if (d <= 0 || d > 64 * MA_MAX_PAIRS || dv <= 0 || nQ <= 0 || nK < 0 || nV < 0 || page_size <= 0 || rot_dims < 0 ||
         rot_dims > d || (rot_dims & 1) || (rot_dims > 0 && !inv_freq))
         return NG_BAD_SIZE;
@@ -158,11 +167,11 @@ NG_EXPORT int ng_qkv_prep(const void* qkv, void* q_out, const float* qw, const f
         NG_LAUNCH((qkv_prep_kernel<__nv_bfloat16>), grid, MA_THREADS, smem, stream, (const __nv_bfloat16*)qkv,
                   (__nv_bfloat16*)q_out, qw, kw, inv_freq, rot_dims, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, table,
                   table_stride, positions, row_entry, nQ, nK, nV, d, dv, page_size, num_pages, eps, status, whole, temp_coef,
-                  temp_every);
+                  temp_every, ld, half_pairing, unit_norm);
     else
         NG_LAUNCH((qkv_prep_kernel<float>), grid, MA_THREADS, smem, stream, (const float*)qkv, (float*)q_out, qw, kw,
                   inv_freq, rot_dims, (float*)k_pages, (float*)v_pages, table, table_stride, positions, row_entry, nQ, nK, nV,
-                  d, dv, page_size, num_pages, eps, status, whole, temp_coef, temp_every);
+                  d, dv, page_size, num_pages, eps, status, whole, temp_coef, temp_every, ld, half_pairing, unit_norm);
     return ng_launch_status();
 }
 
@@ -170,7 +179,7 @@ NG_EXPORT int ng_qkv_prep(const void* qkv, void* q_out, const float* qw, const f
 struct MaParams {
     const void* q; const void* k_pages; const void* v_pages; const int* table; int table_stride;
     const int* positions; const int* row_entry; void* out; int out_ld; float* partial;
-    int nH, nG, d, dv, page_size, num_pages, window, keep_first, n_splits;
+    int nH, nG, d, dv, page_size, num_pages, window, keep_first, n_splits, chunk;
     float scale, softcap, lambda, post_scale, eps; int head_norm;
     const float* slopes; const float* sinks;            // per head, or null
 };
@@ -275,7 +284,8 @@ mapped_attention_kernel(const MaParams p) {
     __syncthreads();
     const int g = head / (p.nH / p.nG);
     const float slope = p.slopes ? p.slopes[head] : 0.f;
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    if (p.chunk > 0) lo = max(lo, (pos / p.chunk) * p.chunk);      // chunks count from the sequence's position 0
     const int n_sink = min(p.keep_first, lo);
     const int n_keys = n_sink + (pos - lo + 1);          // logical key t: position t (t < n_sink) or lo + t - n_sink
     int t0 = 0, t1 = n_keys;
@@ -476,14 +486,14 @@ NG_EXPORT int ng_mapped_attention(const void* q, const void* k_pages, const void
                                   float* partial, int n_rows, int nH, int nG, int n_maps, int d, int dv, int page_size,
                                   int num_pages, int window, int keep_first, int n_splits, float scale, float softcap,
                                   float lambda, float post_scale, float eps, int head_norm, const float* slopes,
-                                  const float* sinks, int act_bf16, cudaStream_t stream) {
+                                  const float* sinks, int chunk, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (d <= 0 || dv <= 0 || dv > 64 * MA_DVU || nH <= 0 || nG <= 0 || nH % nG || page_size <= 0 || n_maps < 1 ||
         n_maps > 2 || n_splits < 1 || n_splits > 65535 || nH > 65535 || (n_splits > 1 && !partial) || out_ld < nH * dv ||
-        window < 0 || keep_first < 0)
+        window < 0 || keep_first < 0 || chunk < 0 || (chunk > 0 && keep_first > 0))
         return NG_BAD_SIZE;
     MaParams p{q, k_pages, v_pages, table, table_stride, positions, row_entry, out, out_ld, n_splits > 1 ? partial : nullptr,
-               nH, nG, d, dv, page_size, num_pages, window, keep_first, n_splits, scale, softcap, lambda, post_scale, eps,
+               nH, nG, d, dv, page_size, num_pages, window, keep_first, n_splits, chunk, scale, softcap, lambda, post_scale, eps,
                head_norm, slopes, sinks};
     if (act_bf16) return n_maps == 2 ? ma_launch<__nv_bfloat16, 2>(p, n_rows, stream) : ma_launch<__nv_bfloat16, 1>(p, n_rows, stream);
     return n_maps == 2 ? ma_launch<float, 2>(p, n_rows, stream) : ma_launch<float, 1>(p, n_rows, stream);
@@ -498,7 +508,7 @@ NG_EXPORT int ng_mapped_attention_merge(float* partial, const int* row_entry, vo
     if (n_rows <= 0) return NG_OK;
     if (!partial || dv <= 0 || dv > 64 * MA_DVU || nH <= 0 || nH > 65535 || n_maps < 1 || n_maps > 2 || n_splits < 1 || out_ld < nH * dv)
         return NG_BAD_SIZE;
-    MaParams p{nullptr, nullptr, nullptr, nullptr, 0, nullptr, row_entry, out, out_ld, partial, nH, 1, 0, dv, 1, 0, 0, 0, n_splits,
+    MaParams p{nullptr, nullptr, nullptr, nullptr, 0, nullptr, row_entry, out, out_ld, partial, nH, 1, 0, dv, 1, 0, 0, 0, n_splits, 0,
                0.f, 0.f, lambda, post_scale, eps, head_norm, nullptr, sinks};
     dim3 grid(n_rows, nH);
     const size_t smem = (size_t)n_maps * dv * sizeof(float);

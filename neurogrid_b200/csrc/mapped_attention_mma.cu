@@ -30,6 +30,7 @@ struct MmaParams {
     const bf16* q; const bf16* k_pages; const bf16* v_pages; const int* table; int table_stride;
     const int* cu_q; const int* ctx_before; bf16* out; int out_ld;
     int nH, nG, page_size, num_pages, window, keep_first;
+    int chunk;                         // > 0: a row sees only the keys of its own chunk of that many positions (counted from 0)
     float scale, softcap, lambda, post_scale, eps; int head_norm;
     float* partial; int n_splits;      // GROUP: runs of keys, their states [row, head, run, map, DV + 2]
     const float* slopes; const float* sinks;    // per head or null: slope * (pos - key position) off every score; exp(sink) in the sum
@@ -126,7 +127,8 @@ mapped_attention_mma_kernel(const MmaParams p) {
         ldsm_x4(qf[ks], Qs + ((size_t)map * ROWS + wt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * QP + ks * 16 + (lane >> 4) * 8);
     // ---- the keys the block's rows see: kept first tokens [0, n_sink), then [lo, last position]
     const int pos_first = before + r0, pos_last = GROUP ? pos_first : before + r0 + n_rows - 1;
-    const int lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    int lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    if (p.chunk > 0) lo = max(lo, (pos_first / p.chunk) * p.chunk);       // the first row's chunk starts earliest
     const int n_sink = min(p.keep_first, lo);
     const int all_keys = n_sink + (pos_last - lo + 1);
     int t_begin = 0, n_keys = all_keys;                  // the block's run of the key list: [t_begin, n_keys)
@@ -141,6 +143,10 @@ mapped_attention_mma_kernel(const MmaParams p) {
     const int w_first = GROUP ? pos_first : pos_first + wt * 16;                     // the warp's positions
     const int w_last = GROUP ? pos_first : min(pos_last, w_first + 15);
     const int w_span = GROUP ? 0 : 15;
+    // chunk starts: of this thread's two rows, and of the warp's first and last row
+    const int cs_a = p.chunk > 0 ? (pos_a / p.chunk) * p.chunk : 0, cs_b = p.chunk > 0 ? (pos_b / p.chunk) * p.chunk : 0;
+    const int cs_first = p.chunk > 0 ? (w_first / p.chunk) * p.chunk : 0;
+    const int cs_last = p.chunk > 0 ? ((w_first + w_span) / p.chunk) * p.chunk : 0;
     const bool warp_live = wt * 16 < n_rows;
     // the distance bias of this thread's two rows, in the softmax's powers of two (GROUP: a row is a head)
     float slope_a = 0.f, slope_b = 0.f;
@@ -213,7 +219,7 @@ mapped_attention_mma_kernel(const MmaParams p) {
             const int k_first = t0 < n_sink ? t0 : lo + (t0 - n_sink);
             const int k_last = t_last < n_sink ? t_last : lo + (t_last - n_sink);
             const bool sink_part = t0 < n_sink;
-            const int w_lo = p.window > 0 ? max(0, w_first - p.window + 1) : 0;     // lowest window key of the warp's rows
+            const int w_lo = max(p.window > 0 ? max(0, w_first - p.window + 1) : 0, cs_first);   // lowest key the warp's rows see
             any = k_first <= w_last && (sink_part || k_last >= w_lo || k_first < p.keep_first);
         }
         if (!any) continue;
@@ -240,6 +246,7 @@ mapped_attention_mma_kernel(const MmaParams p) {
             const int k_first = tile_first, k_last = k_first + KT - 1;
             interior = t0 + KT <= n_keys && (t0 >= n_sink || t0 + KT <= n_sink) && (GROUP || wt * 16 + 15 < n_rows) &&
                        k_last <= w_first && (p.window <= 0 || w_first + w_span - k_first < p.window || k_last < p.keep_first) &&
+                       k_first >= cs_last &&
                        !tile_bad_s[it % 3][0] && !tile_bad_s[it % 3][1];
         }
         constexpr float LOG2E = 1.4426950408889634f;
@@ -258,7 +265,8 @@ mapped_attention_mma_kernel(const MmaParams p) {
                 if (!interior) {
                     const int kpos = kpos_t[j * 8 + 2 * tq + (e & 1)];
                     const bool row_ok = ((e < 2) ? row_a : row_b) < n_rows;
-                    const bool vis = row_ok && kpos >= 0 && kpos <= pos && (p.window <= 0 || pos - kpos < p.window || kpos < p.keep_first);
+                    const bool vis = row_ok && kpos >= ((e < 2) ? cs_a : cs_b) && kpos <= pos &&
+                                     (p.window <= 0 || pos - kpos < p.window || kpos < p.keep_first);
                     v = vis ? v : -INFINITY;
                 }
                 s[j][e] = v;
@@ -395,13 +403,14 @@ NG_EXPORT int ng_mapped_attention_mma(const void* q, const void* k_pages, const 
                                       int n_entries, int max_q, int nH, int nG, int n_maps, int d, int dv, int page_size,
                                       int num_pages, int window, int keep_first, float scale, float softcap, float lambda,
                                       float post_scale, float eps, int head_norm, const float* slopes, const float* sinks,
-                                      cudaStream_t stream) {
+                                      int chunk, cudaStream_t stream) {
     if (n_entries <= 0 || max_q <= 0) return NG_OK;
     if (d != D || dv != DV || nH <= 0 || nG <= 0 || nH % nG || page_size <= 0 || n_maps < 1 || n_maps > 2 || out_ld < nH * dv ||
-        window < 0 || keep_first < 0 || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+        window < 0 || keep_first < 0 || chunk < 0 || (chunk > 0 && keep_first > 0) || ((uintptr_t)q & 15) ||
+        ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
         return NG_BAD_SIZE;
     MmaParams p{(const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before, (bf16*)out,
-                out_ld, nH, nG, page_size, num_pages, window, keep_first, scale, softcap, lambda, post_scale, eps, head_norm,
+                out_ld, nH, nG, page_size, num_pages, window, keep_first, chunk, scale, softcap, lambda, post_scale, eps, head_norm,
                 nullptr, 1, slopes, sinks};
     return n_maps == 2 ? mma_launch<2, false>(p, n_entries, max_q, stream) : mma_launch<1, false>(p, n_entries, max_q, stream);
 }
@@ -414,14 +423,15 @@ NG_EXPORT int ng_mapped_attention_group(const void* q, const void* k_pages, cons
                                         int table_stride, const int* cu_q, const int* ctx_before, float* partial,
                                         int n_entries, int n_splits, int nH, int nG, int n_maps, int d, int dv, int page_size,
                                         int num_pages, int window, int keep_first, float scale, float softcap,
-                                        const float* slopes, cudaStream_t stream) {
+                                        const float* slopes, int chunk, cudaStream_t stream) {
     if (n_entries <= 0) return NG_OK;
     if (d != D || dv != DV || nH <= 0 || nG <= 0 || nH % nG || nH / nG > 16 || page_size <= 0 || n_maps < 1 || n_maps > 2 ||
-        window < 0 || keep_first < 0 || n_splits < 1 || n_splits > 65535 || !partial || ((uintptr_t)q & 15) ||
+        window < 0 || keep_first < 0 || chunk < 0 || (chunk > 0 && keep_first > 0) || n_splits < 1 || n_splits > 65535 || !partial ||
+        ((uintptr_t)q & 15) ||
         ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
         return NG_BAD_SIZE;
     MmaParams p{(const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before, nullptr, 0,
-                nH, nG, page_size, num_pages, window, keep_first, scale, softcap, 0.f, 1.f, 0.f, 0, partial, n_splits, slopes,
+                nH, nG, page_size, num_pages, window, keep_first, chunk, scale, softcap, 0.f, 1.f, 0.f, 0, partial, n_splits, slopes,
                 nullptr};
     return n_maps == 2 ? mma_launch<2, true>(p, n_entries, 1, stream) : mma_launch<1, true>(p, n_entries, 1, stream);
 }

@@ -75,21 +75,25 @@ moe_router_kernel(const T* __restrict__ x, const float* __restrict__ wr, const f
 }
 
 template <typename T>
-__global__ void moe_scale_kernel(T* __restrict__ act, const float* __restrict__ weights, int n_rows, int E, int ff, int ld) {
+__global__ void moe_scale_kernel(T* __restrict__ act, const float* __restrict__ weights, int n_rows, int E, int ff, int ld,
+                                 int ldw, int cols) {
+    // columns behind E*ff (a shared expert's) are reached only when its gate, weights[row, E], multiplies them
     ng_pdl_trigger();
     ng_pdl_wait();
     const int row = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= E * ff) return;
+    if (c >= cols) return;
     T* p = act + (size_t)row * ld + c;
-    ng_st(p, ng_ld(p) * weights[(size_t)row * E + c / ff]);
+    ng_st(p, ng_ld(p) * weights[(size_t)row * ldw + (c < E * ff ? c / ff : E)]);
 }
 
 // out[row, c] = silu(gate_up[row, c]) * gate_up[row, I + c] * (c < E*ff ? weights[row, c / ff] : 1): the SwiGLU of all
-// experts side by side with the routing weight applied at once (steps whose gate/up product has no fused epilogue)
+// experts side by side with the routing weight applied at once (steps whose gate/up product has no fused epilogue).
+// `shared_gated`: the columns behind E*ff (a shared expert's) are multiplied by weights[row, E].  Rows of `weights`
+// lie ldw apart.
 template <typename T>
 __global__ void moe_swiglu_scaled_kernel(const T* __restrict__ gate_up, const float* __restrict__ weights,
-                                         T* __restrict__ out, int I, int E, int ff) {
+                                         T* __restrict__ out, int I, int E, int ff, int ldw, int shared_gated) {
     ng_pdl_trigger();
     ng_pdl_wait();
     const int row = blockIdx.y;
@@ -98,13 +102,13 @@ __global__ void moe_swiglu_scaled_kernel(const T* __restrict__ gate_up, const fl
     const float g = ng_ld(gate_up + (size_t)row * 2 * I + c), u = ng_ld(gate_up + (size_t)row * 2 * I + I + c);
     T act;
     ng_st(&act, g / (1.f + expf(-g)) * u);           // rounded as the unweighted activation is, then weighted
-    const float w = c < E * ff ? weights[(size_t)row * E + c / ff] : 1.f;
+    const float w = c < E * ff ? weights[(size_t)row * ldw + c / ff] : (shared_gated ? weights[(size_t)row * ldw + E] : 1.f);
     ng_st(out + (size_t)row * I + c, ng_ld(&act) * w);
 }
 
 // the same, eight columns a thread with 16-byte accesses (bfloat16; I and ff multiples of 8, so that the eight share an expert)
 __global__ void moe_swiglu_scaled_vec_kernel(const __nv_bfloat16* __restrict__ gate_up, const float* __restrict__ weights,
-                                             __nv_bfloat16* __restrict__ out, int I, int E, int ff) {
+                                             __nv_bfloat16* __restrict__ out, int I, int E, int ff, int ldw, int shared_gated) {
     ng_pdl_trigger();
     ng_pdl_wait();
     const int row = blockIdx.y;
@@ -112,7 +116,7 @@ __global__ void moe_swiglu_scaled_vec_kernel(const __nv_bfloat16* __restrict__ g
     if (c >= I) return;
     const uint4 gv = *reinterpret_cast<const uint4*>(gate_up + (size_t)row * 2 * I + c);
     const uint4 uv = *reinterpret_cast<const uint4*>(gate_up + (size_t)row * 2 * I + I + c);
-    const float w = c < E * ff ? weights[(size_t)row * E + c / ff] : 1.f;
+    const float w = c < E * ff ? weights[(size_t)row * ldw + c / ff] : (shared_gated ? weights[(size_t)row * ldw + E] : 1.f);
     const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&gv);
     const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&uv);
     uint4 ov;
@@ -127,21 +131,22 @@ __global__ void moe_swiglu_scaled_vec_kernel(const __nv_bfloat16* __restrict__ g
 }
 
 NG_EXPORT int ng_moe_swiglu_scaled(const void* gate_up, const float* weights, void* out, int n_rows, int I, int E, int ff,
-                                   int act_bf16, cudaStream_t stream) {
+                                   int ldw, int shared_gated, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
-    if (E <= 0 || ff <= 0 || I < E * ff || n_rows > 65535) return NG_BAD_SIZE;
+    if (E <= 0 || ff <= 0 || I < E * ff || n_rows > 65535 || ldw < E + (shared_gated ? 1 : 0)) return NG_BAD_SIZE;
     if (act_bf16 && I % 8 == 0 && ff % 8 == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         dim3 vgrid((I / 8 + 127) / 128, n_rows);
         NG_LAUNCH((moe_swiglu_scaled_vec_kernel), vgrid, 128, 0, stream, (const __nv_bfloat16*)gate_up, weights,
-                  (__nv_bfloat16*)out, I, E, ff);
+                  (__nv_bfloat16*)out, I, E, ff, ldw, shared_gated);
         return ng_launch_status();
     }
     dim3 grid((I + 255) / 256, n_rows);
     if (act_bf16)
         NG_LAUNCH((moe_swiglu_scaled_kernel<__nv_bfloat16>), grid, 256, 0, stream, (const __nv_bfloat16*)gate_up, weights,
-                  (__nv_bfloat16*)out, I, E, ff);
+                  (__nv_bfloat16*)out, I, E, ff, ldw, shared_gated);
     else
-        NG_LAUNCH((moe_swiglu_scaled_kernel<float>), grid, 256, 0, stream, (const float*)gate_up, weights, (float*)out, I, E, ff);
+        NG_LAUNCH((moe_swiglu_scaled_kernel<float>), grid, 256, 0, stream, (const float*)gate_up, weights, (float*)out, I, E, ff,
+                  ldw, shared_gated);
     return ng_launch_status();
 }
 
@@ -160,15 +165,16 @@ NG_EXPORT int ng_moe_router(const void* x, const float* wr, const float* br, flo
     return ng_launch_status();
 }
 
-NG_EXPORT int ng_moe_scale(void* act, const float* weights, int n_rows, int E, int ff, int ld, int act_bf16,
-                           cudaStream_t stream) {
+NG_EXPORT int ng_moe_scale(void* act, const float* weights, int n_rows, int E, int ff, int ld, int ldw, int shared_gated,
+                           int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
-    if (E <= 0 || ff <= 0 || ld < E * ff || n_rows > 65535) return NG_BAD_SIZE;
-    dim3 grid((E * ff + 255) / 256, n_rows);
+    if (E <= 0 || ff <= 0 || ld < E * ff || n_rows > 65535 || ldw < E + (shared_gated ? 1 : 0)) return NG_BAD_SIZE;
+    const int cols = shared_gated ? ld : E * ff;
+    dim3 grid((cols + 255) / 256, n_rows);
     if (act_bf16)
-        NG_LAUNCH((moe_scale_kernel<__nv_bfloat16>), grid, 256, 0, stream, (__nv_bfloat16*)act, weights, n_rows, E, ff, ld);
+        NG_LAUNCH((moe_scale_kernel<__nv_bfloat16>), grid, 256, 0, stream, (__nv_bfloat16*)act, weights, n_rows, E, ff, ld, ldw, cols);
     else
-        NG_LAUNCH((moe_scale_kernel<float>), grid, 256, 0, stream, (float*)act, weights, n_rows, E, ff, ld);
+        NG_LAUNCH((moe_scale_kernel<float>), grid, 256, 0, stream, (float*)act, weights, n_rows, E, ff, ld, ldw, cols);
     return ng_launch_status();
 }
 
@@ -179,11 +185,13 @@ NG_EXPORT int ng_moe_scale(void* act, const float* weights, int n_rows, int E, i
 //   scores the lower index wins, for groups and for experts).  The top_k chosen experts are weighted by their scores s
 //   (without the correction) over their sum + 1e-20.  Output: dense weights [n_rows, ldw], zero for experts a row does
 //   not use; with `wsg` (float32 [H]) column E receives sigmoid(wsg . x), the gate of a shared expert.
+//   `softmax_scores`: s = softmax(W_r x) over all experts instead of the sigmoid.  `group_max`: a group's score is its
+//   largest choice score.  `route_scale` multiplies the weights.
 template <typename T>
 __global__ void __launch_bounds__(512)
 moe_router_sigmoid_kernel(const T* __restrict__ x, const float* __restrict__ wr, const float* __restrict__ corr,
                           const float* __restrict__ wsg, float* __restrict__ weights, int H, int E, int ldw, int top_k,
-                          int n_groups, int keep_groups) {
+                          int n_groups, int keep_groups, int softmax_scores, int group_max, float route_scale) {
     extern __shared__ float z[];               // [E] scores s, [E] choice scores, [n_groups] group scores
     float* choice = z + E;
     float* gscore = choice + E;
@@ -208,11 +216,27 @@ moe_router_sigmoid_kernel(const T* __restrict__ x, const float* __restrict__ wr,
         acc = ng_warp_sum(acc);
         if (lane == 0) {
             const float s = 1.f / (1.f + expf(-acc));
-            if (e < E) { z[e] = s; choice[e] = s + (corr ? corr[e] : 0.f); out[e] = 0.f; }
+            if (e < E) { z[e] = softmax_scores ? acc : s; choice[e] = s + (corr ? corr[e] : 0.f); out[e] = 0.f; }
             else out[E] = s;
         }
     }
     __syncthreads();
+    if (softmax_scores) {                  // the first warp: largest logit, the exponentials' sum in index order per lane
+        if (warp == 0) {
+            float mx = -INFINITY;
+            for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+            mx = ng_warp_max(mx);
+            float sum = 0.f;
+            for (int e = lane; e < E; e += 32) sum += expf(z[e] - mx);
+            sum = ng_warp_sum(sum);
+            for (int e = lane; e < E; e += 32) {
+                const float s = expf(z[e] - mx) / sum;
+                z[e] = s;
+                choice[e] = s + (corr ? corr[e] : 0.f);
+            }
+        }
+        __syncthreads();
+    }
     const int per = E / n_groups;
     for (int g = threadIdx.x; g < n_groups; g += blockDim.x) {
         float a = -INFINITY, b = -INFINITY;             // the two largest of the group
@@ -220,7 +244,7 @@ moe_router_sigmoid_kernel(const T* __restrict__ x, const float* __restrict__ wr,
             const float v = choice[e];
             if (v > a) { b = a; a = v; } else if (v > b) b = v;
         }
-        gscore[g] = per > 1 ? a + b : a;
+        gscore[g] = per > 1 && !group_max ? a + b : a;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -249,13 +273,13 @@ moe_router_sigmoid_kernel(const T* __restrict__ x, const float* __restrict__ wr,
             idx[k] = best;
             sum += z[best];
         }
-        for (int k = 0; k < top_k; ++k) out[idx[k]] = z[idx[k]] / (sum + 1e-20f);
+        for (int k = 0; k < top_k; ++k) out[idx[k]] = z[idx[k]] / (sum + 1e-20f) * route_scale;
     }
 }
 
 NG_EXPORT int ng_moe_router_sigmoid(const void* x, const float* wr, const float* corr, const float* wsg, float* weights,
-                                    int n_rows, int H, int E, int ldw, int top_k, int n_groups, int keep_groups, int act_bf16,
-                                    cudaStream_t stream) {
+                                    int n_rows, int H, int E, int ldw, int top_k, int n_groups, int keep_groups,
+                                    int softmax_scores, int group_max, float route_scale, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (H <= 0 || E <= 0 || top_k < 1 || top_k > E || top_k > MOE_MAX_TOP || E > 4096 || n_groups < 1 || E % n_groups ||
         keep_groups < 1 || keep_groups > n_groups || top_k > keep_groups * (E / n_groups) || ldw < E + (wsg ? 1 : 0))
@@ -264,10 +288,10 @@ NG_EXPORT int ng_moe_router_sigmoid(const void* x, const float* wr, const float*
     const int threads = n_rows <= 64 ? 32 * (E < 4 ? 4 : E > 16 ? 16 : E) : 128;
     if (act_bf16)
         NG_LAUNCH((moe_router_sigmoid_kernel<__nv_bfloat16>), n_rows, threads, smem, stream, (const __nv_bfloat16*)x, wr, corr,
-                  wsg, weights, H, E, ldw, top_k, n_groups, keep_groups);
+                  wsg, weights, H, E, ldw, top_k, n_groups, keep_groups, softmax_scores, group_max, route_scale);
     else
         NG_LAUNCH((moe_router_sigmoid_kernel<float>), n_rows, threads, smem, stream, (const float*)x, wr, corr, wsg, weights, H,
-                  E, ldw, top_k, n_groups, keep_groups);
+                  E, ldw, top_k, n_groups, keep_groups, softmax_scores, group_max, route_scale);
     return ng_launch_status();
 }
 

@@ -391,16 +391,19 @@ def qkv_prep(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Te
              inv_freq: Optional[torch.Tensor], k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
              table: torch.Tensor, positions: torch.Tensor, row_entry: torch.Tensor, n_q: int, n_k: int, n_v: int,
              dim: int, vdim: int, eps: float, status: torch.Tensor, *, whole: bool = False, q_temp_coef: float = 0.0,
-             q_temp_every: int = 1) -> None:
+             q_temp_every: int = 1, half_pairing: bool = False, unit_norm: bool = False) -> None:
     """qkv[N, (n_q + n_k) * dim + n_v * vdim]: every q and k head (a map of a head counts as one) gets its RMS norm
     over ``dim`` (if its weight is given; float32, shared by all heads) and the rotation of its first
     2 * len(inv_freq) coordinates in pairs (2i, 2i+1) by position * inv_freq[i]; q -> q_out[N, n_q * dim],
     k -> k_pages[P, n_k, page, dim], v -> v_pages[P, n_v, page, vdim].  n_k = n_v = 0 (no pages): a layer that
     reads another layer's keys and values.  ``whole``: ONE norm over all of a row's q (n_q * dim values) and one over
     all of its k, the weights then float32 [n_q * dim] and [n_k * dim].  ``q_temp_coef`` c, ``q_temp_every`` m: q is
-    multiplied by 1 + c * ln(floor((position + 1) / m) + 1) after its norm."""
+    multiplied by 1 + c * ln(floor((position + 1) / m) + 1) after its norm.  ``half_pairing``: the rotated coordinates
+    pair as (i, i + rot_dims/2).  ``unit_norm`` (without norm weights): every q and k head is divided by its root mean
+    square all the same.  ``qkv`` may have further columns behind v; they are not read."""
     n = q_out.shape[0]
-    if q_out.shape != (n, n_q * dim) or qkv.shape != (n, (n_q + n_k) * dim + n_v * vdim) or qkv.dtype != q_out.dtype:
+    if q_out.shape != (n, n_q * dim) or qkv.dim() != 2 or qkv.shape[0] != n \
+            or qkv.shape[1] < (n_q + n_k) * dim + n_v * vdim or qkv.dtype != q_out.dtype:
         raise KernelError("qkv_prep: shapes or dtypes do not fit")
     page_size = num_pages = 1
     if n_k or n_v:
@@ -414,11 +417,12 @@ def qkv_prep(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Te
     if whole and (q_weight is None or q_weight.numel() != n_q * dim or (n_k and (k_weight is None or k_weight.numel() != n_k * dim))):
         raise KernelError("qkv_prep: a norm over the whole projection needs weights of the projection's length")
     f = _fn("mapped_attention", "ng_qkv_prep", [_c_void_p] * 5 + [_c_int] + [_c_void_p] * 3 + [_c_int] + [_c_void_p] * 2
-            + [_c_int] * 8 + [_c_float, _c_void_p, _c_int, _c_float, _c_int, _c_int, _c_void_p])
+            + [_c_int] * 8 + [_c_float, _c_void_p, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p])
     _check(f(_ptr(qkv), _ptr(q_out), _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), rot_dims,
              _ptr(k_pages) if n_k else None, _ptr(v_pages) if n_v else None, _ptr(table), table.shape[1], _ptr(positions),
              _ptr(row_entry), n, n_q, n_k, n_v, dim, vdim, page_size, num_pages, float(eps), _ptr(status),
-             int(bool(whole)), float(q_temp_coef), int(q_temp_every), _act_flag(q_out, "q_out"), _stream()), "qkv_prep")
+             int(bool(whole)), float(q_temp_coef), int(q_temp_every), qkv.shape[1], int(bool(half_pairing)),
+             int(bool(unit_norm)), _act_flag(q_out, "q_out"), _stream()), "qkv_prep")
 
 
 def mapped_attention_partial_floats(n_rows: int, n_heads: int, n_maps: int, vdim: int, n_splits: int) -> int:
@@ -429,7 +433,7 @@ def mapped_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                      positions: torch.Tensor, row_entry: torch.Tensor, out: torch.Tensor, n_heads: int, n_maps: int,
                      window: Optional[int], keep_first: int, scale: float, softcap: float, lam: float, head_norm: bool,
                      post_scale: float, eps: float, n_splits: int = 1, partial: Optional[torch.Tensor] = None,
-                     slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> None:
+                     slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
     """Attention with float32 scores and weights over keys [P, G * n_maps, page, dim] and values [P, G, page, vdim]:
     per head and map m, a_m = softmax(cap(scale * q_m . k_m)) v over the keys j <= pos with pos - j < window or
     j < keep_first (window None: all), cap(s) = softcap * tanh(s / softcap) (softcap 0: none); the head's output is
@@ -438,7 +442,8 @@ def mapped_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     every row's keys into runs, a block each, merged through ``partial`` (float32,
     ``mapped_attention_partial_floats`` values): for steps of few rows.  ``slopes`` (float32 [n_heads]): slope[head] *
     (position - key position) is taken off every score; ``sinks`` (float32 [n_heads]): every softmax's denominator
-    also holds exp(sink[head]), a term that has no key and no value."""
+    also holds exp(sink[head]), a term that has no key and no value.  ``chunk`` > 0: a row also sees only the keys of
+    its own chunk, floor(j / chunk) = floor(pos / chunk)."""
     n = q.shape[0]
     num_pages, n_k, page_size, dim = k_pages.shape
     n_g, vdim = v_pages.shape[1], v_pages.shape[3]
@@ -451,12 +456,12 @@ def mapped_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     if need and (partial is None or partial.numel() < need):
         raise KernelError(f"mapped_attention: the runs need {need} float32 values")
     f = _fn("mapped_attention", "ng_mapped_attention", [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int, _c_void_p]
-            + [_c_int] * 11 + [_c_float] * 5 + [_c_int, _c_void_p, _c_void_p, _c_int, _c_void_p])
+            + [_c_int] * 11 + [_c_float] * 5 + [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p])
     _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(positions), _ptr(row_entry),
              out.data_ptr(), _column_block(out, "attention out"), _ptr(partial) if need else None, n, n_heads, n_g, n_maps,
              dim, vdim, page_size, num_pages, int(window or 0), int(keep_first), int(n_splits), float(scale),
              float(softcap or 0.0), float(lam), float(post_scale), float(eps), int(bool(head_norm)),
-             _slopes(slopes, n_heads), _slopes(sinks, n_heads), _act_flag(q, "q"), _stream()), "mapped_attention")
+             _slopes(slopes, n_heads), _slopes(sinks, n_heads), int(chunk or 0), _act_flag(q, "q"), _stream()), "mapped_attention")
 
 
 MAPPED_BACKEND = os.environ.get("NEUROGRID_B200_MAPPED", "mma")     # "mma": tensor-core kernel for long bfloat16 steps; "ffma"
@@ -472,7 +477,7 @@ def mapped_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
                          cu_q: torch.Tensor, ctx_before: torch.Tensor, out: torch.Tensor, n_entries: int, max_q: int,
                          n_heads: int, n_maps: int, window: Optional[int], keep_first: int, scale: float, softcap: float,
                          lam: float, head_norm: bool, post_scale: float, eps: float,
-                         slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> None:
+                         slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
     """``mapped_attention`` for long bfloat16 steps on the tensor cores: scores are float32 sums of exact bfloat16
     products, the float32 softmax weights enter the weighted sum as three bfloat16 terms each.  Rows are named by
     ``cu_q`` [R+1] and ``ctx_before`` [R]; ``max_q`` bounds the longest entry."""
@@ -485,12 +490,12 @@ def mapped_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
         raise KernelError("mapped_attention_mma: shapes or dtypes do not fit")
     _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before")
     f = _fn("mapped_attention_mma", "ng_mapped_attention_mma", [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 12
-            + [_c_float] * 5 + [_c_int, _c_void_p, _c_void_p, _c_void_p], {"NG_MA_D": dim, "NG_MA_DV": vdim})
+            + [_c_float] * 5 + [_c_int, _c_void_p, _c_void_p, _c_int, _c_void_p], {"NG_MA_D": dim, "NG_MA_DV": vdim})
     _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before),
              out.data_ptr(), _column_block(out, "attention out"), n_entries, max_q, n_heads, n_g, n_maps, dim, vdim,
              page_size, num_pages, int(window or 0), int(keep_first), float(scale), float(softcap or 0.0), float(lam),
-             float(post_scale), float(eps), int(bool(head_norm)), _slopes(slopes, n_heads), _slopes(sinks, n_heads), _stream()),
-           "mapped_attention_mma")
+             float(post_scale), float(eps), int(bool(head_norm)), _slopes(slopes, n_heads), _slopes(sinks, n_heads),
+             int(chunk or 0), _stream()), "mapped_attention_mma")
 
 
 def mapped_attention_group_takes(dim: int, vdim: int, n_heads: int, n_kv_heads: int, dtype) -> bool:
@@ -503,7 +508,7 @@ def mapped_attention_group(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
                            partial: torch.Tensor, n_entries: int, n_heads: int, n_maps: int, window: Optional[int],
                            keep_first: int, scale: float, softcap: float, lam: float, head_norm: bool, post_scale: float,
                            eps: float, n_splits: int, slopes: Optional[torch.Tensor] = None,
-                           sinks: Optional[torch.Tensor] = None) -> None:
+                           sinks: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
     """``mapped_attention`` for a step whose entries bring one token each (bfloat16), on the tensor cores: the query
     heads of a KV group are the rows of a tile, every row's keys are cut into ``n_splits`` runs (a block each), and the
     runs' states pass through ``partial`` (float32, ``mapped_attention_partial_floats`` values, also for one run) to
@@ -521,10 +526,10 @@ def mapped_attention_group(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
     _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(row_entry, "row_entry")
     defines = {"NG_MA_D": dim, "NG_MA_DV": vdim}
     f = _fn("mapped_attention_mma", "ng_mapped_attention_group", [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 11
-            + [_c_float] * 2 + [_c_void_p, _c_void_p], defines)
+            + [_c_float] * 2 + [_c_void_p, _c_int, _c_void_p], defines)
     _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before), _ptr(partial),
              n_entries, int(n_splits), n_heads, n_g, n_maps, dim, vdim, page_size, num_pages, int(window or 0), int(keep_first),
-             float(scale), float(softcap or 0.0), _slopes(slopes, n_heads), _stream()), "mapped_attention_group")
+             float(scale), float(softcap or 0.0), _slopes(slopes, n_heads), int(chunk or 0), _stream()), "mapped_attention_group")
     g = _fn("mapped_attention", "ng_mapped_attention_merge", [_c_void_p] * 3 + [_c_int] * 6 + [_c_float] * 3
             + [_c_int, _c_void_p, _c_int, _c_void_p])
     _check(g(_ptr(partial), _ptr(row_entry), out.data_ptr(), _column_block(out, "attention out"), n, n_heads, n_maps, vdim,
@@ -600,23 +605,57 @@ def retention_chunked_takes(key_dim: int, value_dim: int) -> bool:
 # ----------------------------------------------------------------------------- latent attention
 def latent_prep(x: torch.Tensor, wq: torch.Tensor, wkv: torch.Tensor, cq_out: torch.Tensor, pages: torch.Tensor,
                 gate_out: torch.Tensor, table: torch.Tensor, positions: torch.Tensor, row_entry: torch.Tensor,
-                n_heads: int, eps: float, status: torch.Tensor) -> None:
-    """x[N, rq+rkv+nH] = c_q raw | c raw | gate logits;  cq_out[N, rq] = rmsnorm(c_q raw) * wq;
-    rmsnorm(c raw) * wkv goes to the row's place in pages[P, 1, page, rp] (columns rkv.. zero);
-    gate_out[N, nH] float32 = sigmoid(gate logits)."""
+                n_heads: int, eps: float, status: torch.Tensor, *, rot: int = 0, inv_freq: Optional[torch.Tensor] = None,
+                half_pairing: bool = False) -> None:
+    """x[N, rq+rkv+rot+nH] = c_q raw | c raw | key part raw | gate logits;  cq_out[N, rq] = rmsnorm(c_q raw) * wq;
+    rmsnorm(c raw) * wkv goes to the row's place in pages[P, 1, page, rp] and behind it the key part (``rot`` columns,
+    not normed), rotated by the row's position in pairs (2i, 2i+1) or (i, i+rot/2) with ``inv_freq`` [rot/2]; the
+    columns behind are zero.  gate_out[N, nH] float32 = sigmoid(gate logits), nH the gate's columns.  ``wkv`` and
+    ``pages`` None: a layer that reads another layer's latents (the row has no c and no key part)."""
     n, rq = cq_out.shape
-    rkv = wkv.numel()
-    num_pages, one, page_size, rp = pages.shape
-    if x.shape != (n, rq + rkv + n_heads) or wq.numel() != rq or one != 1 or rp < rkv \
-            or gate_out.shape != (n, n_heads) or cq_out.dtype != x.dtype or pages.dtype != x.dtype:
+    rkv = wkv.numel() if wkv is not None else 0
+    num_pages, one, page_size, rp = pages.shape if pages is not None else (0, 1, 1, 0)
+    if x.shape != (n, rq + rkv + rot + n_heads) or wq.numel() != rq or one != 1 or rp < rkv + rot \
+            or gate_out.shape != (n, n_heads) or cq_out.dtype != x.dtype or (pages is not None and pages.dtype != x.dtype) \
+            or (rkv == 0) != (pages is None) or (rot and (inv_freq is None or inv_freq.numel() != rot // 2 or not rkv)):
         raise KernelError("latent_prep: shapes or dtypes do not fit")
-    _f32(wq, "dq norm"), _f32(wkv, "dkv norm"), _f32(gate_out, "gate")
+    _f32(wq, "dq norm"), _f32(wkv, "dkv norm"), _f32(gate_out, "gate"), _f32(inv_freq, "inv_freq")
     _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry"), _i32(status, "status")
     f = _fn("latent", "ng_latent_prep", [_c_void_p] * 7 + [_c_int] + [_c_void_p] * 2 + [_c_int] * 7
-            + [_c_float, _c_void_p, _c_int, _c_void_p])
+            + [_c_float, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p])
     _check(f(_ptr(x), _ptr(wq), _ptr(wkv), _ptr(cq_out), _ptr(pages), _ptr(gate_out), _ptr(table), table.shape[1],
              _ptr(positions), _ptr(row_entry), n, rq, rkv, rp, n_heads, page_size, num_pages, float(eps),
-             _ptr(status), _act_flag(x, "latent input"), _stream()), "latent_prep")
+             _ptr(status), int(rot), _ptr(inv_freq) if rot else None, int(bool(half_pairing)),
+             _act_flag(x, "latent input"), _stream()), "latent_prep")
+
+
+def latent_rope_q(q: torch.Tensor, positions: torch.Tensor, row_entry: torch.Tensor, inv_freq: torch.Tensor,
+                  n_heads: int, offset: int, half_pairing: bool = False) -> None:
+    """q[N, nH * rp]: columns offset..offset + 2 len(inv_freq) of every head are rotated in place by the row's position,
+    in pairs (2i, 2i+1) or (i, i + rot/2); angles float32."""
+    n = q.shape[0]
+    rp, rot = q.shape[1] // n_heads, 2 * inv_freq.numel()
+    if q.shape[1] != n_heads * rp or offset + rot > rp:
+        raise KernelError("latent_rope_q: shapes do not fit")
+    _f32(inv_freq, "inv_freq"), _i32(positions, "positions"), _i32(row_entry, "row_entry")
+    f = _fn("latent", "ng_latent_rope_q", [_c_void_p] * 4 + [_c_int] * 7 + [_c_void_p])
+    _check(f(_ptr(q), _ptr(positions), _ptr(row_entry), _ptr(inv_freq), n, n_heads, rp, int(offset), rot,
+             int(bool(half_pairing)), _act_flag(q, "q"), _stream()), "latent_rope_q")
+
+
+def head_up_gate(o: torch.Tensor, w: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[N, nH * dv] = (W[h] o[N, h, :rank]) * gate for o [N, nH * rp] and W [nH, dv, rank] of the activation type,
+    gate float32 [N, nH * dv] or None; float32 sums, one rounding.  ``out`` may be a block of columns of a wider buffer."""
+    n = o.shape[0]
+    n_heads, dv, rank = w.shape
+    rp = o.shape[1] // n_heads
+    if o.shape[1] != n_heads * rp or rank > rp or out.shape != (n, n_heads * dv) or w.dtype != o.dtype or out.dtype != o.dtype \
+            or (gate is not None and gate.shape != (n, n_heads * dv)):
+        raise KernelError("head_up_gate: shapes or dtypes do not fit")
+    _f32(gate, "gate")
+    f = _fn("latent", "ng_head_up_gate", [_c_void_p] * 4 + [_c_int] * 7 + [_c_void_p])
+    _check(f(_ptr(o), _ptr(w), _ptr(gate), out.data_ptr(), n, n_heads, rp, rank, dv, _column_block(out, "head_up_gate out"),
+             _act_flag(o, "weighted latents"), _stream()), "head_up_gate")
 
 
 def latent_core_takes(n_heads: int, rank: int) -> bool:
@@ -817,14 +856,117 @@ def softcap_(x: torch.Tensor, cap: float) -> None:
     _check(f(_ptr(x), x.numel(), 1, float(cap), 0, _stream()), "softcap")
 
 
+def gate_mul(y: torch.Tensor, gate: Optional[torch.Tensor], activation: str = "sigmoid", scale: float = 1.0) -> None:
+    """y[N, I] <- y * act(gate) * scale in place, act sigmoid, silu or (``gate`` None) nothing; float32 math.  Both may
+    be blocks of columns of wider buffers."""
+    n, I = y.shape
+    act = 0 if gate is None else {"sigmoid": 1, "silu": 2}[activation]
+    if gate is not None and (gate.shape != y.shape or gate.dtype != y.dtype):
+        raise KernelError("gate_mul: the gate must have the shape and dtype of what it multiplies")
+    f = _fn("elementwise", "ng_gate_mul", [_c_void_p, _c_void_p] + [_c_int] * 5 + [_c_float, _c_int, _c_void_p])
+    _check(f(y.data_ptr(), gate.data_ptr() if gate is not None else None, n, I, _column_block(y, "gate_mul y"),
+             _column_block(gate, "gate_mul gate") if gate is not None else 0, act, float(scale), _act_flag(y, "gate_mul y"),
+             _stream()), "gate_mul")
+
+
+def hc_step(streams: torch.Tensor, n_streams: int, *, x0: Optional[torch.Tensor] = None, delta: Optional[torch.Tensor] = None,
+            mix: Optional[torch.Tensor] = None, out_w: Optional[torch.Tensor] = None, in_w: Optional[torch.Tensor] = None,
+            norm_w: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+            sum_out: Optional[torch.Tensor] = None, eps: float = 0.0, act_dtype=None) -> None:
+    """What lies between two sublayers of a model whose residual stream is ``n_streams`` copies, streams[N, S * H]
+    float32.  ``x0`` [N,H] float32: every copy is x0 (a sequence's start).  ``delta`` (the output y of the sublayer
+    before: [N,H] of the activation dtype or a float32 stack of partial sums) with ``mix`` [S,S] ([from, to]) and
+    ``out_w`` [S]: x_t <- sum_s mix[s,t] x_s + out_w[t] y for all t at once.  ``in_w`` [S] with ``norm_w`` [H] and
+    ``out`` [N,H]: out = rmsnorm(sum_t in_w[t] x_t) * norm_w.  ``sum_out`` [N,H] float32: the sum of the copies."""
+    n = streams.shape[0]
+    H = streams.shape[1] // n_streams
+    if streams.shape[1] != n_streams * H:
+        raise KernelError("hc_step: the streams do not divide into copies")
+    _f32(streams, "streams"), _f32(x0, "x0"), _f32(mix, "mix"), _f32(out_w, "out_w"), _f32(in_w, "in_w"), _f32(norm_w, "norm weight")
+    _f32(sum_out, "sum_out")
+    act_dtype = out.dtype if out is not None else (act_dtype or torch.float32)
+    act = int(act_dtype == torch.bfloat16)
+    d32, n_part, stride = 0, 1, 0
+    if delta is not None:
+        d32, n_part, stride = _maybe_stack(delta, n, H, act_dtype, "hc_step delta")
+        if mix is None or mix.numel() != n_streams * n_streams or out_w is None or out_w.numel() != n_streams:
+            raise KernelError("hc_step: an update needs the mixing matrix and the output weights")
+    if in_w is not None and (in_w.numel() != n_streams or norm_w is None or norm_w.numel() != H or out is None or out.shape != (n, H)):
+        raise KernelError("hc_step: the read-out needs its weights, the norm's weight and an output [N, H]")
+    for t in (x0, sum_out):
+        if t is not None and t.shape != (n, H):
+            raise KernelError("hc_step: x0 and sum_out are [N, H]")
+    f = _fn("hyper", "ng_hc_step", [_c_void_p] * 3 + [_c_int, _c_int, _c_ll] + [_c_void_p] * 6 + [_c_int] * 3
+            + [_c_float, _c_int, _c_void_p])
+    _check(f(_ptr(streams), _ptr(x0), _ptr(delta), d32, n_part, stride, _ptr(mix), _ptr(out_w), _ptr(in_w), _ptr(norm_w),
+             _ptr(out), _ptr(sum_out), n, int(n_streams), H, float(eps), act, _stream()), "hc_step")
+
+
+# ----------------------------------------------------------------------------- gated linear attention
+GATED_LINEAR_CHUNK = 32      # tokens of a chunk in the chunk-by-chunk kernels
+
+
+def gated_linear(x: torch.Tensor, z: torch.Tensor, norm_w: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
+                 cu_q: torch.Tensor, ctx_before: torch.Tensor, slots: torch.Tensor, n_entries: int, n_heads: int,
+                 key_dim: int, value_dim: int, tau: float, eps: float, out_scale: float = 1.0,
+                 scratch: Optional[torch.Tensor] = None, state_scratch: Optional[torch.Tensor] = None, max_q: int = 0) -> None:
+    """x[N, 2*nH*(dk+dv)] = q|k|v|g and z[N, nH*dk] (decay logits);  per head S = diag(alpha) S + k v^T with
+    alpha = sigmoid(z)^(1/tau) per key channel, o = S^T (q dk^(-1/2)), out = o/rms(o) * norm_w * silu(g) * out_scale;
+    state[slots, nH, dk, dv] float32.  ``out`` [N, nH*dv] of the activation dtype may be a block of columns of a wider
+    buffer.  With ``scratch`` (float32 [N, nH*dv]), ``state_scratch`` (``gated_linear_chunked_scratch`` float32 values)
+    and ``max_q`` (the longest portion) the kernels for long portions run, which regroup the sums chunk by chunk
+    (``gated_linear_chunked_takes`` tells whether they take the head sizes); else the token-by-token kernel."""
+    n = x.shape[0]
+    if x.shape[1] != 2 * n_heads * (key_dim + value_dim) or z.shape != (n, n_heads * key_dim) or z.dtype != x.dtype \
+            or out.shape != (n, n_heads * value_dim) or out.dtype != x.dtype or norm_w.numel() != value_dim \
+            or state.shape[1:] != (n_heads, key_dim, value_dim):
+        raise KernelError("gated_linear: shapes or dtypes do not fit")
+    _f32(norm_w, "head norm weight"), _f32(state, "state"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(slots, "slots")
+    _f32(scratch, "scratch"), _f32(state_scratch, "state scratch")
+    ldo = _column_block(out, "gated_linear out")
+    act = _act_flag(x, "gated_linear input")
+    if scratch is not None:
+        need = gated_linear_chunked_scratch(n, n_entries, n_heads, key_dim, value_dim)
+        if scratch.shape != (n, n_heads * value_dim) or state_scratch is None or state_scratch.numel() < need or max_q <= 0:
+            raise KernelError(f"gated_linear: the chunked kernels need a scratch of the output's shape, {need} float32 "
+                              "values for the chunks' states and the longest portion's length")
+        f = _fn("gated_linear", "ng_gated_linear_chunked", [_c_void_p] * 10 + [_c_int] * 6 + [_c_float] * 3 + [_c_int, _c_int, _c_void_p])
+        _check(f(_ptr(x), _ptr(z), _ptr(norm_w), _ptr(state), out.data_ptr(), _ptr(scratch), _ptr(state_scratch), _ptr(cu_q),
+                 _ptr(ctx_before), _ptr(slots), n_entries, n, int(max_q), n_heads, key_dim, value_dim, float(tau), float(eps),
+                 float(out_scale), ldo, act, _stream()), "gated_linear (chunked)")
+        return
+    f = _fn("gated_linear", "ng_gated_linear", [_c_void_p] * 8 + [_c_int] * 4 + [_c_float] * 3 + [_c_int, _c_int, _c_void_p])
+    _check(f(_ptr(x), _ptr(z), _ptr(norm_w), _ptr(state), out.data_ptr(), _ptr(cu_q), _ptr(ctx_before), _ptr(slots), n_entries,
+             n_heads, key_dim, value_dim, float(tau), float(eps), float(out_scale), ldo, act, _stream()), "gated_linear")
+
+
+def gated_linear_chunked_scratch(n_rows: int, n_entries: int, n_heads: int, key_dim: int, value_dim: int) -> int:
+    """float32 values the chunked kernels need: per chunk and head the state before it and the chunk's whole decay."""
+    return (n_rows // GATED_LINEAR_CHUNK + n_entries + 1) * n_heads * (key_dim * value_dim + key_dim)
+
+
+def gated_linear_chunked_takes(key_dim: int, value_dim: int) -> bool:
+    """Whether the chunk-by-chunk kernels take the head sizes."""
+    return False
+
+
+def scale_(x: torch.Tensor, factor: float) -> None:
+    """x <- x * factor in place (float32 logits)."""
+    _f32(x, "logits")
+    f = _fn("elementwise", "ng_unary", [_c_void_p, _c_ll, _c_int, _c_float, _c_int, _c_void_p])
+    _check(f(_ptr(x), x.numel(), 2, float(factor), 0, _stream()), "scale")
+
+
 # ----------------------------------------------------------------------------- routed experts
 def moe_router_sigmoid(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor],
                        w_shared_gate: Optional[torch.Tensor], weights: torch.Tensor, top_k: int, n_groups: int = 1,
-                       keep_groups: int = 1) -> None:
+                       keep_groups: int = 1, *, softmax_scores: bool = False, group_max: bool = False,
+                       route_scale: float = 1.0) -> None:
     """weights[N, E (+1)] float32: scores s = sigmoid(W_r x); the top_k experts by s + correction among the experts
     of the keep_groups best of n_groups groups of neighbours (a group's score: its two largest choice scores) get
     s / (sum of the chosen s + 1e-20), the others zero.  With ``w_shared_gate`` (float32 [H]) the last column
-    receives sigmoid(w . x)."""
+    receives sigmoid(w . x).  ``softmax_scores``: s = softmax(W_r x) over all experts instead; ``group_max``: a group's
+    score is its largest choice score; ``route_scale`` multiplies the weights."""
     n, H = x.shape
     E = w_router.shape[0]
     ldw = weights.shape[1]
@@ -832,9 +974,10 @@ def moe_router_sigmoid(x: torch.Tensor, w_router: torch.Tensor, correction: Opti
             or (correction is not None and correction.numel() != E) or (w_shared_gate is not None and w_shared_gate.numel() != H):
         raise KernelError("moe_router_sigmoid: shapes do not fit")
     _f32(w_router, "router weight"), _f32(correction, "correction"), _f32(w_shared_gate, "shared gate"), _f32(weights, "weights")
-    f = _fn("moe", "ng_moe_router_sigmoid", [_c_void_p] * 5 + [_c_int] * 8 + [_c_void_p])
+    f = _fn("moe", "ng_moe_router_sigmoid", [_c_void_p] * 5 + [_c_int] * 9 + [_c_float, _c_int, _c_void_p])
     _check(f(_ptr(x), _ptr(w_router), _ptr(correction), _ptr(w_shared_gate), _ptr(weights), n, H, E, ldw, int(top_k),
-             int(n_groups), int(keep_groups), _act_flag(x, "router input"), _stream()), "moe_router_sigmoid")
+             int(n_groups), int(keep_groups), int(bool(softmax_scores)), int(bool(group_max)), float(route_scale),
+             _act_flag(x, "router input"), _stream()), "moe_router_sigmoid")
 
 
 def moe_clamped_glu_scaled(gate_up: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, n_experts: int, expert_ff: int,
@@ -866,27 +1009,31 @@ def moe_router(x: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch
              _stream()), "moe_router")
 
 
-def moe_scale(act: torch.Tensor, weights: torch.Tensor, expert_ff: int) -> None:
-    """act[N, ld]: columns e*ff..(e+1)*ff are multiplied by weights[N, e], in place; columns behind E*ff stay."""
+def moe_scale(act: torch.Tensor, weights: torch.Tensor, expert_ff: int, shared_gated: bool = False) -> None:
+    """act[N, ld]: columns e*ff..(e+1)*ff are multiplied by weights[N, e], in place; columns behind E*ff stay, or, with
+    ``shared_gated`` (weights then has a column E), are multiplied by weights[N, E]."""
     n, ld = act.shape
-    E = weights.shape[1]
+    E = weights.shape[1] - int(bool(shared_gated))
     if weights.shape[0] != n or ld < E * expert_ff:
         raise KernelError("moe_scale: shapes do not fit")
     _f32(weights, "routing weights")
-    f = _fn("moe", "ng_moe_scale", [_c_void_p, _c_void_p] + [_c_int] * 5 + [_c_void_p])
-    _check(f(_ptr(act), _ptr(weights), n, E, int(expert_ff), ld, _act_flag(act, "moe act"), _stream()), "moe_scale")
+    f = _fn("moe", "ng_moe_scale", [_c_void_p, _c_void_p] + [_c_int] * 7 + [_c_void_p])
+    _check(f(_ptr(act), _ptr(weights), n, E, int(expert_ff), ld, weights.shape[1], int(bool(shared_gated)),
+             _act_flag(act, "moe act"), _stream()), "moe_scale")
 
 
-def moe_swiglu_scaled(gate_up: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, expert_ff: int) -> None:
-    """out[N, I] = silu(gate_up[:, :I]) * gate_up[:, I:], columns e*ff..(e+1)*ff times weights[N, e] (float32)."""
+def moe_swiglu_scaled(gate_up: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, expert_ff: int,
+                      shared_gated: bool = False) -> None:
+    """out[N, I] = silu(gate_up[:, :I]) * gate_up[:, I:], columns e*ff..(e+1)*ff times weights[N, e] (float32); with
+    ``shared_gated`` the columns behind E*ff times weights[N, E]."""
     n, I = out.shape
-    E = weights.shape[1]
+    E = weights.shape[1] - int(bool(shared_gated))
     if gate_up.shape != (n, 2 * I) or gate_up.dtype != out.dtype or weights.shape[0] != n or I < E * expert_ff:
         raise KernelError("moe_swiglu_scaled: shapes do not fit")
     _f32(weights, "routing weights")
-    f = _fn("moe", "ng_moe_swiglu_scaled", [_c_void_p] * 3 + [_c_int] * 5 + [_c_void_p])
-    _check(f(_ptr(gate_up), _ptr(weights), _ptr(out), n, I, E, int(expert_ff), _act_flag(out, "moe act"), _stream()),
-           "moe_swiglu_scaled")
+    f = _fn("moe", "ng_moe_swiglu_scaled", [_c_void_p] * 3 + [_c_int] * 7 + [_c_void_p])
+    _check(f(_ptr(gate_up), _ptr(weights), _ptr(out), n, I, E, int(expert_ff), weights.shape[1], int(bool(shared_gated)),
+             _act_flag(out, "moe act"), _stream()), "moe_swiglu_scaled")
 
 
 # ----------------------------------------------------------------------------- per-layer token input

@@ -42,6 +42,9 @@ def model_from_dir(model_dir: str, *, dtype, device):
     """(config, model) for the folder's config.json and safetensors."""
     dtype = parse_dtype(dtype)
     cfg = load_config(model_dir)
+    if hasattr(cfg, "with_shapes"):          # an architecture some of whose sizes only the tensors' shapes give
+        from ..weights.safetensors_io import index_model_dir
+        cfg = cfg.with_shapes({name: tuple(e.shape) for name, e in index_model_dir(model_dir).items()})
     spec = cfg.model_spec()
     weights = load_weights(model_dir, declare_tensors(spec))
     return cfg, build_model(spec, weights, dtype=dtype, device=device)

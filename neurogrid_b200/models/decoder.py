@@ -90,6 +90,8 @@ class Decoder:
         """Libraries of this package the model launches: the embedding's and the head's, and what
         every part declares (``kernels()``; a part that declares nothing launches nothing here)."""
         jobs = [("elementwise", None), ("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None)]
+        if self.spec.streams:
+            jobs.append(("hyper", None))
         for part in list(self.blocks) + [self.final_norm]:
             jobs += getattr(part, "kernels", list)()
         return jobs
@@ -105,7 +107,7 @@ class Decoder:
         # scratch that a part keeps per row besides its products' outputs (a part says so with scratch_bytes_per_row())
         extra = max((getattr(part, "scratch_bytes_per_row", lambda: 0)() for b in self.blocks for part in (b.mixer, b.ffn)),
                     default=0)
-        return 8 * self.spec.hidden + e * self.spec.hidden + 2 * e * widest + extra
+        return 8 * self.spec.hidden * max(1, self.spec.streams) + e * self.spec.hidden + 2 * e * widest + extra
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
@@ -143,9 +145,11 @@ class Decoder:
     # The same in pieces, for a caller that runs some stretches of the schedule as CUDA graphs and
     # others (parts that are not ``graph_safe``) eagerly between them.
     def begin(self, ctx: StepContext) -> torch.Tensor:
-        """The float32 residual stream [N, H] holding the embeddings of the step's tokens."""
+        """The float32 residual stream [N, H] holding the embeddings of the step's tokens.  A model whose stream is
+        several copies (``spec.streams``) gets [N, streams * H], not yet filled: the embeddings go to a buffer of their
+        own, from which the first block's first kernel makes every copy."""
         s = self.spec
-        h = ctx.ws.buf("residual", ctx.n_rows, s.hidden, torch.float32)
+        h = ctx.ws.buf("embedded" if s.streams else "residual", ctx.n_rows, s.hidden, torch.float32)
         ops.embed(self.embed_table, ctx.tokens, h, ctx.status, scale=s.embed_scale)
         if self.position_table is not None:                  # learned absolute positions: h += table[position]
             ops.embed(self.position_table, ctx.positions, h, ctx.status, accumulate=True)
@@ -155,19 +159,41 @@ class Decoder:
                 raise RuntimeError("the model keeps each request's previous token: the step must hand it that state")
             ops.pair_embed(self.pair_table, ctx.tokens, ctx.model_cache.state, ctx.cu_q, ctx.ctx_before, ctx.slots,
                            ctx.row_entry, h, ctx.n_entries, s.vocab_size, tp.buckets, tp.mul_prev, tp.mul_cur, ctx.status)
+        if s.streams:
+            return ctx.ws.buf("residual", ctx.n_rows, s.streams * s.hidden, torch.float32)
         return h
 
     def run_entries(self, ctx: StepContext, caches: List[object], entries, h: torch.Tensor, pending):
         """Schedule entries ``entries`` (indices), in order; takes and returns the feed-forward
         output that is not yet added to the stream."""
         sched = self.spec.schedule
+        if self.spec.streams and pending is None:            # the schedule's start: every copy is the embedding output
+            from ..parts.block import HyperStart
+            pending = HyperStart(ctx.ws.buf("embedded", ctx.n_rows, self.spec.hidden, torch.float32))
         for i in entries:
             pending = self.blocks[sched[i].layer].forward(h, pending, ctx, caches[i])
         return pending
 
+    def collapse(self, ctx: StepContext, h: torch.Tensor, pending) -> torch.Tensor:
+        """For a model whose stream is several copies: the last sublayer's output is written into the copies and
+        their sum [N, H] float32 is returned (what the final norm reads)."""
+        from ..parts.block import HyperStart
+        s = self.spec
+        total = ctx.ws.buf("stream_sum", h.shape[0], s.hidden, torch.float32)
+        if isinstance(pending, HyperStart):
+            ops.hc_step(h, s.streams, x0=pending.x0, sum_out=total, act_dtype=self.dtype)
+        elif pending is None:
+            ops.hc_step(h, s.streams, sum_out=total, act_dtype=self.dtype)
+        else:
+            ops.hc_step(h, s.streams, delta=pending.y, mix=pending.mix, out_w=pending.out_w, sum_out=total,
+                        act_dtype=self.dtype)
+        return total
+
     def finish(self, ctx: StepContext, h: torch.Tensor, pending, want_rows: Optional[torch.Tensor],
                n_want: int) -> Optional[torch.Tensor]:
         s = self.spec
+        if s.streams:
+            h, pending = self.collapse(ctx, h, pending), None
         if n_want == 0:
             if pending is not None:
                 ops.residual_add(h, pending)     # keeps the stream whole for callers that inspect it
@@ -178,6 +204,8 @@ class Decoder:
         ops.linear(x, self.head_weight, None, logits)
         if s.logit_softcap:
             ops.softcap_(logits, s.logit_softcap)
+        if s.logit_scale != 1.0:
+            ops.scale_(logits, s.logit_scale)
         return logits
 
     def graph_pieces(self):
@@ -209,6 +237,7 @@ class _BlockSpec:
         self.mixer_norm, self.ffn_norm = layer.mixer_norm, layer.ffn_norm
         self.names = layer.names
         self.options = layer.options
+        self.prefix = layer.prefix
 
 
 def _join(full_name: str, rel: str) -> str:

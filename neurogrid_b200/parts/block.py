@@ -250,3 +250,117 @@ class ParallelBlock:
         if fused:
             return ops.linear_to_residual(inner, self.w_out, None, ctx.ws, "parallel_out", residual=h)
         return ops.linear_to_residual(inner, self.w_out, self.b_out, ctx.ws, "parallel_out")
+
+
+class HyperPending:
+    """What a hyper block leaves for the kernel after it: its last sublayer's output (not yet written into the copies of
+    the stream) with the mixing matrix and output weights that write it."""
+
+    def __init__(self, y, mix, out_w, eps):
+        self.y, self.mix, self.out_w, self.eps = y, mix, out_w, eps
+
+
+@register("block", "hyper")
+class HyperBlock:
+    """Pre-norm with hyper-connections: the residual stream is S copies x_1..x_S (``spec.options["streams"]``).  For
+    sublayer q (the mixer, then the feed-forward if there is one), with vectors in_q, out_q [S] and a matrix mix_q [S,S]:
+
+        u = sum_s in_q[s] x_s;   y = sublayer(norm_q(u));   x_t <- sum_s mix_q[s, t] x_s + out_q[t] y   (all t at once)
+
+    The copies are float32 [N, S * H] (the buffer the model hands over as its stream).  One kernel does what lies
+    between two sublayers: the update by the sublayer before (also the last one of the layer before, handed over as
+    ``pending``), the read-out u and its norm.  The first block of a model receives the embedding output as
+    ``pending.x0``: every copy starts as that.  Sublayers hand their outputs over (an activation tensor or a stack of
+    float32 partial sums); they never add into the stream themselves, since every copy takes the output times a
+    weight of its own."""
+
+    def __init__(self, spec, *, dtype, device, owns_cache=True):
+        self.spec, self.dtype, self.device = spec, dtype, device
+        self.streams = int(spec.options["streams"])
+        kw = dict(dtype=dtype, device=device)
+        mixer_kw = dict(kw)
+        if not owns_cache:
+            mixer_kw["owns_cache"] = False
+        self.mixer = registry.build("mixer", spec.mixer, **mixer_kw)
+        self.ffn = registry.build("ffn", spec.ffn, **kw) if spec.ffn is not None else None
+        self.mixer_norm = registry.build("norm", spec.mixer_norm, **kw)
+        self.ffn_norm = registry.build("norm", spec.ffn_norm, **kw) if spec.ffn is not None else None
+        self.hc = {}
+
+    def parts(self):
+        n = self.spec.names
+        roles = {"mixer": self.mixer, "ffn": self.ffn, "mixer_norm": self.mixer_norm, "ffn_norm": self.ffn_norm}
+        return {n[r]: p for r, p in roles.items() if p is not None}
+
+    def _hc_names(self):
+        n = self.spec.names
+        return [n["mixer_hc"]] + ([n["ffn_hc"]] if self.ffn is not None else [])
+
+    def tensors(self):
+        from ..weights.decl import TensorDecl
+        out, S = {}, self.streams
+        for sub, part in self.parts().items():
+            for name, decl in part.tensors().items():
+                out[f"{sub}.{name}" if name else sub] = decl
+        for hc in self._hc_names():
+            out[hc + ".in"] = TensorDecl((S,), "share")
+            out[hc + ".out"] = TensorDecl((S,), "norm")
+            out[hc + ".mix"] = TensorDecl((S, S), "eye")
+        return out
+
+    def bind(self, t):
+        import torch
+        for sub, part in self.parts().items():
+            pre = sub + "."
+            own = {k[len(pre):]: v for k, v in t.items() if k.startswith(pre)}
+            if sub in t:
+                own[""] = t[sub]
+            part.bind(own)
+        f32 = dict(device=self.device, dtype=torch.float32)
+        for hc in self._hc_names():
+            self.hc[hc] = tuple(t[f"{hc}.{k}"].to(**f32).contiguous() for k in ("in", "out", "mix"))
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def kernels(self):
+        return [("hyper", None)] + [job for p in self.parts().values() for job in getattr(p, "kernels", list)()]
+
+    @property
+    def graph_safe(self):
+        return all(getattr(p, "graph_safe", False) for p in self.parts().values())
+
+    def _between(self, X, pending, hc, norm, buf):
+        """The update by the sublayer before, then the read-out through ``hc``'s weights and ``norm``."""
+        from ..csrc import ops
+        w_in = self.hc[hc][0]
+        kw = dict(in_w=w_in, norm_w=norm.weight, out=buf, eps=norm.spec.eps)
+        if isinstance(pending, HyperStart):
+            ops.hc_step(X, self.streams, x0=pending.x0, **kw)
+        elif pending is None:
+            ops.hc_step(X, self.streams, **kw)
+        else:
+            ops.hc_step(X, self.streams, delta=pending.y, mix=pending.mix, out_w=pending.out_w, **kw)
+        return buf
+
+    def forward(self, X, pending, ctx, cache):
+        n = X.shape[0]
+        H = X.shape[1] // self.streams
+        buf = ctx.ws.buf("normed", n, H, self.dtype)
+        ctx.residual = None                                  # sublayers hand their outputs over
+        names = self._hc_names()
+        x = self._between(X, pending, names[0], self.mixer_norm, buf)
+        y = self.mixer.forward(x, ctx, cache)
+        pending = HyperPending(y, self.hc[names[0]][2], self.hc[names[0]][1], self.spec.mixer_norm.eps)
+        if self.ffn is not None:
+            x = self._between(X, pending, names[1], self.ffn_norm, buf)
+            y = self.ffn.forward(x, ctx)
+            pending = HyperPending(y, self.hc[names[1]][2], self.hc[names[1]][1], self.spec.ffn_norm.eps)
+        return pending
+
+
+class HyperStart:
+    """Handed to a model's first hyper block: every copy of the stream starts as ``x0`` [N, H] float32."""
+
+    def __init__(self, x0):
+        self.x0 = x0

@@ -43,10 +43,13 @@ class MappedAttention:
         self.whole = getattr(spec, "norm_scope", "head") == "projection"      # one norm over all of q, one over all of k
 
     def _proj(self):
+        """The stacked projection's parts in order: q, k, v (a layer that reads another's cache: q only), then the
+        output gate's logits if the mixer has one."""
         s = self.spec
         rows = {"q": s.n_heads * s.n_maps * s.key_dim, "k": s.n_kv_heads * s.n_maps * s.key_dim,
-                "v": s.n_kv_heads * s.value_dim}
-        return {p: rows[p] for p in (("q", "k", "v") if self.owns_cache else ("q",))}
+                "v": s.n_kv_heads * s.value_dim, "out_gate": s.n_heads * s.value_dim}
+        parts = ("q", "k", "v") if self.owns_cache else ("q",)
+        return {p: rows[p] for p in parts + (("out_gate",) if getattr(s, "out_gate", False) else ())}
 
     def tensors(self):
         s, n = self.spec, self.spec.names
@@ -56,7 +59,7 @@ class MappedAttention:
             for p, rows in self._proj().items():
                 d[n[p + "_bias"]] = TensorDecl((rows,), "bias")
             d[n["o_bias"]] = TensorDecl((s.hidden,), "bias")
-        if s.qk_norm:
+        if s.qk_norm and getattr(s, "norm_weight", True):
             rows = self._proj()
             d[n["q_norm"]] = TensorDecl((rows["q"] if self.whole else s.key_dim,), "norm")
             if self.owns_cache:
@@ -77,7 +80,7 @@ class MappedAttention:
         if s.bias:
             self.b_qkv = torch.cat([t[n[p + "_bias"]].to(**kw) for p in self._proj()]).contiguous()
             self.b_o = t[n["o_bias"]].to(**kw).contiguous()
-        if s.qk_norm:
+        if s.qk_norm and getattr(s, "norm_weight", True):
             self.q_norm = t[n["q_norm"]].to(**f32).contiguous()
             if self.owns_cache:
                 self.k_norm = t[n["k_norm"]].to(**f32).contiguous()
@@ -106,6 +109,8 @@ class MappedAttention:
     def _longest(self, cache):
         s = self.spec
         longest = cache.table.shape[1] * cache.k_pages.shape[2]
+        if getattr(s, "chunk", None):
+            return min(longest, s.chunk)
         return min(longest, s.window + s.keep_first) if s.window else longest
 
     def _group_splits(self, n_rows, cache):
@@ -130,16 +135,15 @@ class MappedAttention:
         s = self.spec
         if n_rows > self.SPLIT_MAX_ROWS:
             return 1
-        longest = cache.table.shape[1] * cache.k_pages.shape[2]
-        if s.window:
-            longest = min(longest, s.window + s.keep_first)
+        longest = self._longest(cache)
         most = min(self.MAX_SPLITS, longest // self.SPLIT_MIN_KEYS)
         if most <= 1 or torch.device(self.device).type != "cuda":       # (the host-side tests step the parts without a GPU)
             return 1
         return max(1, min(most, -(-6 * ops.sm_count(self.device) // max(1, n_rows * s.n_heads))))
 
-    def core(self, x, ctx, cache, out):
-        """out[N, n_heads * value_dim] (may be a block of columns of a wider buffer): the heads' outputs."""
+    def core(self, x, ctx, cache, out, out_scale=1.0):
+        """out[N, n_heads * value_dim] (may be a block of columns of a wider buffer): the heads' outputs (gated, if the
+        mixer has an output gate), times ``out_scale``."""
         s = self.spec
         n = x.shape[0]
         if cache.writes and not self.owns_cache:
@@ -149,26 +153,30 @@ class MappedAttention:
         n_k, n_v = (s.n_kv_heads * s.n_maps, s.n_kv_heads) if self.owns_cache else (0, 0)
         qkv = ctx.ws.buf("mattn_qkv", n, self.w_qkv.shape[0], self.dtype)
         ops.linear(x, self.w_qkv, self.b_qkv, qkv)
+        gated = getattr(s, "out_gate", False)
+        gate = qkv[:, qkv.shape[1] - s.n_heads * s.value_dim:] if gated else None        # the gate's logits: the last columns
         if self.owns_cache and not writes:       # has k/v weights but this run reads another cache: the q columns only
             q_only = ctx.ws.buf("mattn_qonly", n, n_q * s.key_dim, self.dtype)
             q_only.copy_(qkv[:, : n_q * s.key_dim])
             qkv, n_k, n_v = q_only, 0, 0
         q = ctx.ws.buf("mattn_q", n, n_q * s.key_dim, self.dtype)
         pa = PositionArgs.of(self.position.kernel_args())
-        if pa.inv_freq is not None and pa.half_pairing:
-            raise NotImplementedError("this mixer rotates pairs (2i, 2i+1)")
         ops.qkv_prep(qkv, q, self.q_norm, self.k_norm if n_k else None, pa.inv_freq, cache.k_pages if n_k else None,
                      cache.v_pages if n_v else None, cache.table, ctx.positions, ctx.row_entry, n_q, n_k, n_v,
                      s.key_dim, s.value_dim, s.eps, ctx.status, whole=self.whole,
-                     q_temp_coef=getattr(s, "q_temp_coef", 0.0), q_temp_every=getattr(s, "q_temp_every", 1))
+                     q_temp_coef=getattr(s, "q_temp_coef", 0.0), q_temp_every=getattr(s, "q_temp_every", 1),
+                     half_pairing=bool(pa.inv_freq is not None and pa.half_pairing),
+                     unit_norm=bool(s.qk_norm and not getattr(s, "norm_weight", True)))
         self.attend(q, cache, ctx, out, pa.score_slopes)
+        if gated or out_scale != 1.0:
+            ops.gate_mul(out, gate, "sigmoid", out_scale)
 
     def attend(self, q, cache, ctx, out, slopes=None):
         """The attention core over the pages: q [N, n_heads * n_maps * key_dim] as the preparation left it.
         ``slopes``: the position encoding's score bias per head, if it has one."""
         s = self.spec
         n = q.shape[0]
-        extra = dict(slopes=slopes, sinks=self.sinks)
+        extra = dict(slopes=slopes, sinks=self.sinks, chunk=getattr(s, "chunk", None) or 0)
         if ctx.max_q == 1 and n <= self.GROUP_MAX_ROWS and not ctx.fixed_launches and \
                 ops.mapped_attention_group_takes(s.key_dim, s.value_dim, s.n_heads, s.n_kv_heads, self.dtype):
             n_splits = self._group_splits(n, cache)

@@ -13,7 +13,8 @@ class MoE:
     """Router logits in float32 (with a bias) -> the top_k experts of each token, weighted by the softmax
     over the chosen logits -> sum of the chosen SwiGLU experts' outputs, plus a shared expert's.  With sigmoid
     scoring the experts are chosen by score plus a stored correction among the best groups of experts and weighted
-    by their scores over the scores' sum; the clamped activation and the shared expert's gate are applied in the
+    by their scores over the scores' sum (the scores may also be a softmax over all experts, a group's score its
+    largest, the weights scaled); the clamped activation and the shared expert's gate are applied in the
     same pass as the routing weights.
 
     Laid out as two products over ALL experts side by side: gate and up rows of every expert (and of
@@ -28,7 +29,7 @@ class MoE:
         self.spec, self.dtype, self.device = spec, dtype, device
         self.width = spec.n_experts * spec.expert_ff + spec.shared_ff
         self.w_gate_up = self.w_down = self.w_router = self.b_router = self.correction = self.w_shared_gate = None
-        self.sigmoid = getattr(spec, "scoring", "softmax") == "sigmoid"
+        self.sigmoid = getattr(spec, "scoring", "softmax") in ("sigmoid", "softmax_all")    # the router kernel with groups
         self.clamped = getattr(spec, "activation", "swiglu") == "clamped_glu"
 
     def _expert_names(self):
@@ -77,7 +78,9 @@ class MoE:
         weights = ctx.ws.buf("moe_weights", n, s.n_experts + (self.w_shared_gate is not None), torch.float32)
         if self.sigmoid:
             ops.moe_router_sigmoid(x, self.w_router, self.correction, self.w_shared_gate, weights, s.top_k, s.n_groups,
-                                   s.keep_groups)
+                                   s.keep_groups, softmax_scores=s.scoring == "softmax_all",
+                                   group_max=getattr(s, "group_score", "top2") == "max",
+                                   route_scale=getattr(s, "route_scale", 1.0))
         else:
             ops.moe_router(x, self.w_router, self.b_router, weights, s.top_k)
         act = ctx.ws.buf("moe_act", n, I, self.dtype)
@@ -88,9 +91,10 @@ class MoE:
                                        self.w_shared_gate is not None)
         elif ops.gemm_sm100_ok(x, self.w_gate_up):
             ops.gemm_swiglu_sm100(x, self.w_gate_up, act)          # the gate rides in the epilogue
-            ops.moe_scale(act, weights, s.expert_ff)
+            ops.moe_scale(act, weights, s.expert_ff, shared_gated=self.w_shared_gate is not None)
         else:
             gu = ctx.ws.buf("moe_gate_up", n, 2 * I, self.dtype)
             ops.linear(x, self.w_gate_up, None, gu)
-            ops.moe_swiglu_scaled(gu, weights, act, s.expert_ff)   # gate and routing weight in one pass
+            ops.moe_swiglu_scaled(gu, weights, act, s.expert_ff,   # gate and routing weight in one pass
+                                  shared_gated=self.w_shared_gate is not None)
         return ops.linear_to_residual(act, self.w_down, None, ctx.ws, "ffn_out", residual=ctx.residual)

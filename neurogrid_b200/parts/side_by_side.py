@@ -1,4 +1,4 @@
-"""Two mixers on one input, their normed outputs averaged."""
+"""Two mixers on one input: their normed outputs averaged, or their outputs in a weighted sum."""
 from __future__ import annotations
 
 import torch
@@ -14,14 +14,24 @@ class SideBySide:
     """y = 0.5 * (rmsnorm(left(x)) * w_left + rmsnorm(right(x)) * w_right): both mixers read the same x, each output is
     divided by its root mean square over the model width and multiplied by a plain weight; sums and norms float32.
     The mixer's cache needs are its parts' needs one after the other (left's, then right's), and it is handed the views
-    in that order.  In a step of few rows the result is added into the float32 stream here."""
+    in that order.  In a step of few rows the result is added into the float32 stream here.
 
-    def __init__(self, spec, *, dtype, device):
+    ``spec.combine`` "weighted": y = left_scale * left(x) + right_scale * right(x).  Both mixers end with a projection
+    into the stream, so their inner activations (each times its scale, in float32, before its one rounding) lie side
+    by side in one buffer and ONE product with the two output matrices side by side along the contraction (stacked
+    when bound) is the weighted sum; both parts must offer ``core``, ``inner_width`` and ``out_weight``."""
+
+    def __init__(self, spec, *, dtype, device, owns_cache=True):
         self.spec, self.dtype, self.device = spec, dtype, device
         kw = dict(dtype=dtype, device=device)
         self.left = registry.build("mixer", spec.left, **kw)
         self.right = registry.build("mixer", spec.right, **kw)
-        self.w_left = self.w_right = None
+        self.w_left = self.w_right = self.w_out = None
+        self.weighted = getattr(spec, "combine", "norm_mean") == "weighted"
+        if self.weighted:
+            for part in (self.left, self.right):
+                if not all(hasattr(part, a) for a in ("core", "inner_width", "out_weight")):
+                    raise ValueError(f"side by side: a weighted sum needs the inner activations of {type(part).__name__}")
 
     def _sides(self):
         n = self.spec.names
@@ -29,7 +39,8 @@ class SideBySide:
 
     def tensors(self):
         s, n = self.spec, self.spec.names
-        out = {n["left_out"]: TensorDecl((s.hidden,), "norm"), n["right_out"]: TensorDecl((s.hidden,), "norm")}
+        out = {} if self.weighted else {n["left_out"]: TensorDecl((s.hidden,), "norm"),
+                                        n["right_out"]: TensorDecl((s.hidden,), "norm")}
         for sub, part in self._sides():
             for name, decl in part.tensors().items():
                 out[f"{sub}.{name}"] = decl
@@ -38,12 +49,22 @@ class SideBySide:
     def bind(self, t):
         n = self.spec.names
         f32 = dict(device=self.device, dtype=torch.float32)
-        self.w_left = t[n["left_out"]].to(**f32).contiguous()
-        self.w_right = t[n["right_out"]].to(**f32).contiguous()
-        own = (n["left_out"], n["right_out"])
+        own = ()
+        if not self.weighted:
+            self.w_left = t[n["left_out"]].to(**f32).contiguous()
+            self.w_right = t[n["right_out"]].to(**f32).contiguous()
+            own = (n["left_out"], n["right_out"])
         for sub, part in self._sides():
             pre = sub + "."
             part.bind({k[len(pre):]: v for k, v in t.items() if k.startswith(pre) and k not in own})
+        if self.weighted:
+            (wl, bl), (wr, br) = self.left.out_weight(), self.right.out_weight()
+            if bl is not None or br is not None:
+                raise ValueError("side by side: a weighted sum takes output projections without biases")
+            self.w_out = torch.cat([wl, wr], dim=1).contiguous()
+            for part in (self.left, self.right):             # the stacked matrix serves; the parts' own copies go
+                if hasattr(part, "drop_out_weight"):
+                    part.drop_out_weight()
 
     @staticmethod
     def _flat(need):
@@ -73,6 +94,12 @@ class SideBySide:
         s = self.spec
         views = list(cache)
         n_left = len(self._flat(self.left.cache_need()))
+        if self.weighted:
+            ka = self.left.inner_width()
+            inner = ctx.ws.buf("side_inner", x.shape[0], self.w_out.shape[1], self.dtype)
+            self.left.core(x, ctx, self._views(self.left.cache_need(), views[:n_left]), inner[:, :ka], out_scale=s.left_scale)
+            self.right.core(x, ctx, self._views(self.right.cache_need(), views[n_left:]), inner[:, ka:], out_scale=s.right_scale)
+            return ops.linear_to_residual(inner, self.w_out, None, ctx.ws, "mixer_out", residual=ctx.residual)
         residual, ctx.residual = ctx.residual, None        # the parts hand their outputs over; the sum is formed here
         try:
             a = self.left.forward(x, ctx, self._views(self.left.cache_need(), views[:n_left]), out_name="side_left")

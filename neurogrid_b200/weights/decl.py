@@ -9,9 +9,9 @@ from typing import Tuple
 @dataclass(frozen=True)
 class TensorDecl:
     shape: Tuple[int, ...]
-    init: str = "matrix"       # matrix | conv | norm | bias  (how random weights are drawn)
+    init: str = "matrix"       # matrix | conv | norm | bias | zeros | eye | share  (how random weights are drawn)
     integer: bool = False      # an integer table (kept as int32) rather than a float tensor
 
     def __post_init__(self):
-        if self.init not in ("matrix", "conv", "norm", "bias", "zeros"):
+        if self.init not in ("matrix", "conv", "norm", "bias", "zeros", "eye", "share"):
             raise ValueError(f"unknown init {self.init!r}")

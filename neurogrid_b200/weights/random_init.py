@@ -1,6 +1,6 @@
 """Random-weights mode: draw every declared tensor from a seed, or write a whole model folder.
 
-Distributions: matrices N(0, 0.02); short-conv kernels N(0, 0.2); norm weights 1 + N(0, 0.1);
+Distributions: matrices N(0, 0.02); "eye" the identity + N(0, 0.02); "share" 1/length + N(0, 0.02); short-conv kernels N(0, 0.2); norm weights 1 + N(0, 0.1);
 biases N(0, 0.02).  Tensors are drawn in sorted-name order from one generator, so a
 (configuration, seed) pair names one model.  The reference has random weights only for its
 INT8 Llama layer (``gpu/engine/layer.cu:260-386``).
@@ -16,7 +16,7 @@ import torch
 from .decl import TensorDecl
 from .safetensors_io import write_file
 
-_STD = {"matrix": 0.02, "conv": 0.2, "norm": 0.1, "bias": 0.02}
+_STD = {"matrix": 0.02, "conv": 0.2, "norm": 0.1, "bias": 0.02, "eye": 0.02, "share": 0.02}
 
 
 def draw(decls: Mapping[str, TensorDecl], seed: int, *, dtype=torch.bfloat16, device="cpu") -> Dict[str, torch.Tensor]:
@@ -34,6 +34,10 @@ def draw(decls: Mapping[str, TensorDecl], seed: int, *, dtype=torch.bfloat16, de
         t = torch.empty(d.shape, dtype=torch.float32, device=device).normal_(0.0, _STD[d.init], generator=gen)
         if d.init == "norm":
             t += 1.0
+        elif d.init == "eye":                 # a square matrix near the identity
+            t += torch.eye(d.shape[0], d.shape[1], device=device)
+        elif d.init == "share":               # weights of a mean: near 1 / length
+            t += 1.0 / max(1, d.shape[0])
         out[name] = t.to(dtype)
     return out
 

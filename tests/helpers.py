@@ -12,6 +12,9 @@ from neurogrid_b200.weights import load_weights
 def make_runner(model_dir, *, dtype=torch.float32, device="cpu", num_pages=64, page_size=16, max_requests=4,
                 max_tokens_per_step=512, max_seq_len=None):
     cfg = load_config(model_dir)
+    if hasattr(cfg, "with_shapes"):
+        from neurogrid_b200.weights.safetensors_io import index_model_dir
+        cfg = cfg.with_shapes({n: tuple(e.shape) for n, e in index_model_dir(model_dir).items()})
     spec = cfg.model_spec()
     weights = load_weights(model_dir, declare_tensors(spec))
     model = build_model(spec, weights, dtype=dtype, device=device)

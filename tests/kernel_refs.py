@@ -72,14 +72,16 @@ def add_layernorm(h, delta, weight, out, eps, rows=None, post=None):
 
 
 def qkv_prep(qkv, q_out, q_weight, k_weight, inv_freq, k_pages, v_pages, table, positions, row_entry, n_q, n_k, n_v,
-             dim, vdim, eps, status, *, whole=False, q_temp_coef=0.0, q_temp_every=1):
+             dim, vdim, eps, status, *, whole=False, q_temp_coef=0.0, q_temp_every=1, half_pairing=False, unit_norm=False):
     n = qkv.shape[0]
     x = qkv.to(D)
     q = x[:, : n_q * dim].reshape(n, n_q, dim)
     k = x[:, n_q * dim:(n_q + n_k) * dim].reshape(n, n_k, dim)
-    v = x[:, (n_q + n_k) * dim:].reshape(n, n_v, vdim)
+    v = x[:, (n_q + n_k) * dim:(n_q + n_k) * dim + n_v * vdim].reshape(n, n_v, vdim)      # columns behind v are the caller's
 
     def norm(t, w):
+        if w is None and unit_norm:
+            return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps)
         if w is None:
             return t
         if whole:                                                 # one norm over all heads of the row
@@ -94,6 +96,10 @@ def qkv_prep(qkv, q_out, q_weight, k_weight, inv_freq, k_pages, v_pages, table, 
         ang = (positions.to(torch.float32)[:, None] * inv_freq[None, :]).to(D)          # float32 angle
         c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
         o = t.clone()
+        if half_pairing:
+            a, b = t[..., :r // 2], t[..., r // 2:r]
+            o[..., :r // 2], o[..., r // 2:r] = a * c - b * s, b * c + a * s
+            return o
         a, b = t[..., 0:r:2], t[..., 1:r:2]
         o[..., 0:r:2], o[..., 1:r:2] = a * c - b * s, b * c + a * s
         return o
@@ -122,7 +128,7 @@ def qkv_prep(qkv, q_out, q_weight, k_weight, inv_freq, k_pages, v_pages, table, 
 
 
 def mapped_attention(q, k_pages, v_pages, table, positions, row_entry, out, n_heads, n_maps, window, keep_first, scale,
-                     softcap, lam, head_norm, post_scale, eps, n_splits=1, partial=None, slopes=None, sinks=None):
+                     softcap, lam, head_norm, post_scale, eps, n_splits=1, partial=None, slopes=None, sinks=None, chunk=0):
     n = q.shape[0]
     P, n_k, ps, dim = k_pages.shape
     n_g, vdim = v_pages.shape[1], v_pages.shape[3]
@@ -134,6 +140,8 @@ def mapped_attention(q, k_pages, v_pages, table, positions, row_entry, out, n_he
             continue
         pos = int(positions[r])
         lo = max(0, pos - window + 1) if window else 0
+        if chunk:
+            lo = max(lo, (pos // chunk) * chunk)
         kp = torch.tensor([j for j in range(pos + 1) if j >= lo or j < keep_first], device=q.device)
         pages = table[e, kp // ps].long()
         K = k_pages[pages, :, kp % ps].to(D)             # [keys, n_g * n_maps, dim]
@@ -239,9 +247,11 @@ def softcap_(x, cap):
     x.copy_((cap * torch.tanh(x.to(D) / cap)).to(x.dtype))
 
 
-def moe_router_sigmoid(x, w_router, correction, w_shared_gate, weights, top_k, n_groups=1, keep_groups=1):
+def moe_router_sigmoid(x, w_router, correction, w_shared_gate, weights, top_k, n_groups=1, keep_groups=1, *,
+                       softmax_scores=False, group_max=False, route_scale=1.0):
     n, E = x.shape[0], w_router.shape[0]
-    s = torch.sigmoid(x.to(D) @ w_router.to(D).T)
+    logits = x.to(D) @ w_router.to(D).T
+    s = torch.softmax(logits, -1) if softmax_scores else torch.sigmoid(logits)
     choice = s + (correction.to(D) if correction is not None else 0.0)
     per = E // n_groups
     weights.zero_()
@@ -250,7 +260,7 @@ def moe_router_sigmoid(x, w_router, correction, w_shared_gate, weights, top_k, n
         if keep_groups < n_groups:
             gs = []
             for g in range(n_groups):
-                top2 = sorted(c[g * per:(g + 1) * per].tolist(), reverse=True)[:2]
+                top2 = sorted(c[g * per:(g + 1) * per].tolist(), reverse=True)[:1 if group_max else 2]
                 gs.append(sum(top2))
             order = sorted(range(n_groups), key=lambda g: (-gs[g], g))
             for g in order[keep_groups:]:
@@ -258,7 +268,7 @@ def moe_router_sigmoid(x, w_router, correction, w_shared_gate, weights, top_k, n
         chosen = sorted(range(E), key=lambda e: (-float(c[e]), e))[:top_k]
         total = sum(float(s[r, e]) for e in chosen) + 1e-20
         for e in chosen:
-            weights[r, e] = float(s[r, e]) / total
+            weights[r, e] = float(s[r, e]) / total * route_scale
     if w_shared_gate is not None:
         weights[:, E] = torch.sigmoid(x.to(D) @ w_shared_gate.to(D)).to(weights.dtype)
 
@@ -412,7 +422,147 @@ def sample(logits, temperature, top_p, uniform, out, scratch):
         out[r] = int(hit[0]) if len(hit) else int(torch.argmax(lg))
 
 
-_NAMES = ["gather_tokens", "embed", "add_rmsnorm", "residual_add", "swiglu", "gemm_f32", "linear", "shortconv", "rope_cache",
+# ------------------------------------------------------------------------------------------------ Dodilix's launchers
+def scale_(x, factor):
+    x.mul_(factor)
+
+
+def gate_mul(y, gate, activation="sigmoid", scale=1.0):
+    f = torch.full_like(y, scale, dtype=D)
+    if gate is not None:
+        g = gate.to(D)
+        f = f * (torch.sigmoid(g) if activation == "sigmoid" else g * torch.sigmoid(g))
+    y.copy_((y.to(D) * f).to(y.dtype))
+
+
+def hc_step(streams, n_streams, *, x0=None, delta=None, mix=None, out_w=None, in_w=None, norm_w=None, out=None, sum_out=None,
+            eps=0.0, act_dtype=None):
+    n, S = streams.shape[0], n_streams
+    H = streams.shape[1] // S
+    X = x0.to(D)[:, None, :].expand(n, S, H).clone() if x0 is not None else streams.to(D).reshape(n, S, H)
+    if delta is not None:
+        y = (delta.sum(0) if delta.dim() == 3 else delta).to(D)
+        X = torch.einsum("st,nsh->nth", mix.to(D).reshape(S, S), X) + out_w.to(D)[None, :, None] * y[:, None, :]
+    if x0 is not None or delta is not None:
+        streams.copy_(X.reshape(n, S * H).to(streams.dtype))
+    if in_w is not None:
+        u = torch.einsum("s,nsh->nh", in_w.to(D), X)
+        out.copy_((u * torch.rsqrt((u * u).mean(-1, keepdim=True) + eps) * norm_w.to(D)).to(out.dtype))
+    if sum_out is not None:
+        sum_out.copy_(X.sum(1).to(sum_out.dtype))
+
+
+def moe_swiglu_scaled(gate_up, weights, out, expert_ff, shared_gated=False):
+    n, I = out.shape
+    E = weights.shape[1] - int(bool(shared_gated))
+    g, u = gate_up[:, :I].to(D), gate_up[:, I:].to(D)
+    w = weights[:, :E].to(D).repeat_interleave(expert_ff, dim=1)
+    tail = weights[:, E:E + 1].to(D) if shared_gated else torch.ones(n, 1, dtype=D)
+    w = torch.cat([w, tail.expand(n, I - E * expert_ff)], dim=1)
+    out.copy_((g * torch.sigmoid(g) * u * w).to(out.dtype))
+
+
+def gated_linear(x, z, norm_w, state, out, cu_q, ctx_before, slots, n_entries, n_heads, key_dim, value_dim, tau, eps,
+                 out_scale=1.0, scratch=None, state_scratch=None, max_q=0):
+    H, dk, dv = n_heads, key_dim, value_dim
+    for e in range(n_entries):
+        r0, r1 = int(cu_q[e]), int(cu_q[e + 1])
+        slot = int(slots[e])
+        S = state[slot].to(D).clone() if int(ctx_before[e]) > 0 else torch.zeros(H, dk, dv, dtype=D)
+        for r in range(r0, r1):
+            row = x[r].to(D)
+            q = row[:H * dk].reshape(H, dk) * dk ** -0.5
+            k = row[H * dk:2 * H * dk].reshape(H, dk)
+            v = row[2 * H * dk:2 * H * dk + H * dv].reshape(H, dv)
+            g = row[2 * H * dk + H * dv:].reshape(H, dv)
+            alpha = torch.sigmoid(z[r].to(D)).pow(1.0 / tau).reshape(H, dk)
+            S = alpha[:, :, None] * S + k[:, :, None] * v[:, None, :]
+            o = torch.einsum("hkv,hk->hv", S, q)
+            o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * norm_w.to(D) * (g * torch.sigmoid(g)) * out_scale
+            out[r] = o.reshape(-1).to(out.dtype)
+        if r1 > r0:
+            state[slot] = S.to(state.dtype)
+
+
+def latent_prep(x, wq, wkv, cq_out, pages, gate_out, table, positions, row_entry, n_heads, eps, status, *, rot=0,
+                inv_freq=None, half_pairing=False):
+    n, rq = cq_out.shape
+    rkv = wkv.numel() if wkv is not None else 0
+    xd = x.to(D)
+    a = xd[:, :rq]
+    cq_out.copy_((a * torch.rsqrt((a * a).mean(-1, keepdim=True) + eps) * wq.to(D)).to(cq_out.dtype))
+    gate_out.copy_(torch.sigmoid(xd[:, rq + rkv + rot:]).to(gate_out.dtype))
+    if not rkv:
+        return
+    c = xd[:, rq:rq + rkv]
+    c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + eps) * wkv.to(D)
+    kr = _rotate_tail(xd[:, rq + rkv:rq + rkv + rot], positions, inv_freq, half_pairing) if rot else xd[:, :0]
+    ps, rp = pages.shape[2], pages.shape[3]
+    for r in range(n):
+        e = int(row_entry[r])
+        if e < 0:
+            continue
+        pos = int(positions[r])
+        page = int(table[e, pos // ps])
+        rowv = torch.zeros(rp, dtype=D)
+        rowv[:rkv], rowv[rkv:rkv + rot] = c[r], kr[r]
+        pages[page, 0, pos % ps] = rowv.to(pages.dtype)
+
+
+def _rotate_tail(t, positions, inv_freq, half_pairing):
+    r = t.shape[-1]
+    ang = (positions.to(torch.float32)[:, None] * inv_freq[None, :]).to(D)
+    c, s = torch.cos(ang), torch.sin(ang)
+    o = t.clone()
+    if half_pairing:
+        a, b = t[..., :r // 2], t[..., r // 2:]
+        o[..., :r // 2], o[..., r // 2:] = a * c - b * s, b * c + a * s
+    else:
+        a, b = t[..., 0::2], t[..., 1::2]
+        o[..., 0::2], o[..., 1::2] = a * c - b * s, b * c + a * s
+    return o
+
+
+def latent_rope_q(q, positions, row_entry, inv_freq, n_heads, offset, half_pairing=False):
+    n = q.shape[0]
+    rot = 2 * inv_freq.numel()
+    qv = q.view(n, n_heads, -1)
+    for h in range(n_heads):
+        qv[:, h, offset:offset + rot] = _rotate_tail(qv[:, h, offset:offset + rot].to(D), positions, inv_freq,
+                                                     half_pairing).to(q.dtype)
+
+
+def latent_core(q, pages, table, positions, row_entry, gate, out, n_heads, window, scale, n_splits=1, partial=None):
+    n = q.shape[0]
+    ps, rp = pages.shape[2], pages.shape[3]
+    for r in range(n):
+        e = int(row_entry[r])
+        if e < 0:
+            out[r] = 0
+            continue
+        pos = int(positions[r])
+        lo = max(0, pos - window + 1) if window else 0
+        kp = torch.arange(lo, pos + 1)
+        C = pages[table[e, kp // ps].long(), 0, kp % ps].to(D)                  # [keys, rp]
+        qr = q[r].to(D).reshape(n_heads, rp)
+        w = torch.softmax(qr @ C.T * scale, -1)
+        o = w @ C
+        if gate is not None:
+            o = o * gate[r].to(D)[:, None]
+        out[r] = o.reshape(-1).to(out.dtype)
+
+
+def head_up_gate(o, w, gate, out):
+    n = o.shape[0]
+    H, dv, rank = w.shape
+    y = torch.einsum("hvr,nhr->nhv", w.to(D), o.to(D).reshape(n, H, -1)[:, :, :rank]).reshape(n, H * dv)
+    if gate is not None:
+        y = y * gate.to(D)
+    out.copy_(y.to(out.dtype))
+
+
+_NAMES = ["scale_", "gate_mul", "hc_step", "moe_swiglu_scaled", "gated_linear", "latent_prep", "latent_rope_q", "latent_core",
+          "head_up_gate", "gather_tokens", "embed", "add_rmsnorm", "residual_add", "swiglu", "gemm_f32", "linear", "shortconv", "rope_cache",
           "attention_generic", "sample", "add_layernorm", "qkv_prep", "mapped_attention", "gated_delta", "pair_embed",
           "pair_norm_mean", "relu_squared_", "softcap_", "moe_router_sigmoid", "moe_clamped_glu_scaled"]
 
