@@ -70,3 +70,16 @@ def fuzelorn_dirs(tmp_path_factory):
         out[name + "_calm"] = fuzelorn_models.write_model(cfg, seed, str(tmp_path_factory.mktemp(f"fuzelorn_{name}c")),
                                                           router_gain=0.02)
     return out
+
+
+@pytest.fixture(scope="session")
+def dodilix_dirs(tmp_path_factory):
+    """Model folders for the tiny Dodilix configurations; "<name>_calm" has routers that hardly look at the token,
+    for comparisons in bfloat16."""
+    import dodilix_models
+    out = {}
+    for name, (cfg, seed) in dodilix_models.CONFIGS.items():
+        out[name] = dodilix_models.write_model(cfg, seed, str(tmp_path_factory.mktemp(f"dodilix_{name}")))
+        out[name + "_calm"] = dodilix_models.write_model(cfg, seed, str(tmp_path_factory.mktemp(f"dodilix_{name}c")),
+                                                         router_gain=0.02)
+    return out

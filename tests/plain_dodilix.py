@@ -96,7 +96,7 @@ def gated_linear_attention(h, w, pre, m, eps, state=None):
 def parallel_mixer(h, w, pre, m, eps):
     left = chunk_attention(h, w, pre + "left.", m["left"], eps)
     right, _ = gated_linear_attention(h, w, pre + "right.", m["right"], eps)
-    return m["left_scale"] * left + m["right_scale"] * right
+    return m.get("left_scale", 1.0) * left + m.get("right_scale", 1.0) * right
 
 
 def latent_kv(h, w, pre, m, eps):
@@ -105,19 +105,19 @@ def latent_kv(h, w, pre, m, eps):
     r = m["kv_rank"]
     d = h @ w[pre + "dkv"].T
     c = rms_norm(d[:, :r], w[pre + "dkv.norm"], eps)
-    kr = rotate(d[:, None, r:], torch.arange(T), m["rot_dim"], m["rot"]["base"], True)[:, 0]
+    kr = rotate(d[:, None, r:], torch.arange(T), m.get("rot_dim", 0), (m.get("rot") or {}).get("base", 1.0), True)[:, 0]
     return c, kr
 
 
 def latent_attention(h, w, pre, m, eps, kv):
     """Causal softmax attention whose keys and values are expanded from ``kv`` = (latent, rotated key part)."""
     T = h.shape[0]
-    H, d, dr, dv = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
+    H, d, dr, dv = m["heads"], m["dim"], m.get("rot_dim", 0), m["vdim"]
     c, kr = kv
     cq = rms_norm(h @ w[pre + "dq"].T, w[pre + "dq.norm"], eps)
     q = (cq @ w[pre + "uq"].T).view(T, H, d + dr)
     qn = q[..., :d]
-    qr = rotate(q[..., d:], torch.arange(T), dr, m["rot"]["base"], True)
+    qr = rotate(q[..., d:], torch.arange(T), dr, (m.get("rot") or {}).get("base", 1.0), True)
     kn = (c @ w[pre + "uk"].T).view(T, H, d)
     v = (c @ w[pre + "uv"].T).view(T, H, dv)
     out = torch.zeros(T, H, dv, dtype=F64)
