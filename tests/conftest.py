@@ -74,12 +74,12 @@ def fuzelorn_dirs(tmp_path_factory):
 
 @pytest.fixture(scope="session")
 def dodilix_dirs(tmp_path_factory):
-    """Model folders for the tiny Dodilix configurations; "<name>_calm" has routers that hardly look at the token,
-    for comparisons in bfloat16."""
+    """Model folders for the tiny Dodilix configurations; in "<name>_calm" a layer's routed experts are all alike, for
+    comparisons in bfloat16 (a router's close call then changes nothing)."""
     import dodilix_models
     out = {}
     for name, (cfg, seed) in dodilix_models.CONFIGS.items():
         out[name] = dodilix_models.write_model(cfg, seed, str(tmp_path_factory.mktemp(f"dodilix_{name}")))
         out[name + "_calm"] = dodilix_models.write_model(cfg, seed, str(tmp_path_factory.mktemp(f"dodilix_{name}c")),
-                                                         router_gain=0.02)
+                                                         same_experts=True)
     return out

@@ -3,8 +3,9 @@
 The weights are drawn so that the mechanisms show in the logits: projections keep activations of order one, the matrices
 behind attention scores are larger (a peaked softmax: a key wrongly seen or missed changes the output), sinks are of the
 scores' size, the decay's bias ranges from forgetful to nearly none, the stream's copies are mixed by matrices far from
-the identity, routers look at the token.  ``router_gain`` small gives routers that hardly look at the token, for
-comparisons in bfloat16, where a close call of the router would otherwise flip an expert."""
+the identity, routers look at the token.  ``same_experts`` gives every routed expert of a layer the weights of its
+first one, for comparisons in bfloat16: a close call of the router, which rounding may decide the other way, then
+changes nothing (the weights still have to sum to the router's scale); the choice itself is tested in float32."""
 from __future__ import annotations
 
 import json
@@ -103,7 +104,7 @@ CONFIGS = {"A": (DODI_A, 41), "B": (DODI_B, 42), "B0": (DODI_B0, 43), "C": (DODI
 PAGE_SIZE = {"A": 8, "B": 16, "B0": 4, "C": 8}
 
 
-def draw_weights(config: dict, seed: int, router_gain: float = 3.0):
+def draw_weights(config: dict, seed: int, router_gain: float = 3.0, same_experts: bool = False):
     """name -> bfloat16 tensor for every tensor the configuration declares."""
     decls = declare_tensors(config_from_dict(config).model_spec())
     g = torch.Generator().manual_seed(seed)
@@ -134,14 +135,19 @@ def draw_weights(config: dict, seed: int, router_gain: float = 3.0):
                     "a1": 2.0, "a2": 2.0}.get(leaf, 1.0)
             t = gain * rnd(d.shape) / d.shape[-1] ** 0.5
         out[name] = t.to(torch.bfloat16)
+    if same_experts:
+        for name in out:
+            parts = name.split(".")
+            if len(parts) == 4 and parts[1] == "mlp" and parts[2][0] == "e" and parts[2][1:].isdigit():
+                out[name] = out[".".join([parts[0], "mlp", "e0", parts[3]])]
     return out
 
 
-def write_model(config: dict, seed: int, folder: str, weights=None, router_gain: float = 3.0) -> str:
+def write_model(config: dict, seed: int, folder: str, weights=None, router_gain: float = 3.0, same_experts: bool = False) -> str:
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(config, f)
-    write_file(os.path.join(folder, "model.safetensors"), weights or draw_weights(config, seed, router_gain))
+    write_file(os.path.join(folder, "model.safetensors"), weights or draw_weights(config, seed, router_gain, same_experts))
     return folder
 
 
