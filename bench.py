@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine at the LFM2-1.2B shape, random weights, one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl ours|reference]
-                    [--shape 1.2b|700m|350m] [--prompt-len N] [--workload mixed350m|long700m|metanex|rofulorn|fuzelorn]
+                    [--shape 1.2b|700m|350m] [--prompt-len N] [--workload mixed350m|long700m|metanex|rofulorn|fuzelorn|dodilix]
 
 A "step" is one decode step of the batch.  The default run has the layer sizes of the
 LFM2-1.2B configuration, a batch of 8 and requests that hold 2,048-token prompts and grow
@@ -1112,6 +1112,208 @@ def fuzelorn_kernel_times(eng, l2, pk):
     return out
 
 
+# ---------------------------------------------------------------------------------------------- --workload dodilix
+def dodilix_config(width, layers):
+    """A Dodilix configuration with layers of a real model's sizes: four copies of the stream; layers alternate between
+    a parallel mixer (chunked attention, heads of 128 with half of each head rotated, four query heads to a key/value
+    head, chunks of 1,024, beside a gated linear attention with as many heads of 128 x 128) and a latent attention
+    (heads of 128 + 64 rotated coordinates, a latent of 192 beside the 64 shared rotated ones, queries through a latent
+    of width/2), every fourth layer reading the latents of the latent layer before it; the first layer's feed-forward
+    dense, the others' routed (16 experts of width/4 in four groups of which two are kept, top 4, a gated shared
+    expert of width/2)."""
+    heads = width // 128
+    left = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+            "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": 64}}
+    right = {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 64}
+    parallel = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.8, "right_scale": 1.1}}
+    latent = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": width // 2, "kv_rank": 192,
+              "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": width // 4}, "shared": {"ff": width // 2}}
+    dense = {"kind": "dense", "ff": 4 * width}
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            layer = dict(parallel)
+        else:
+            layer = {"type": "latent_attention", "mixer": dict(latent, **({"kv_from": i - 2} if i % 4 == 3 else {}))}
+        layer["mlp"] = dense if i == 0 else moe
+        out.append(layer)
+    return {"architecture": "Dodilix", "vocab": 65536, "width": width, "streams": 4, "norm": {"eps": 1e-5},
+            "logit_scale": 0.25, "embedding": {"scale": 2.0}, "layers": out}
+
+
+def run_dodilix(args):
+    """Prefill and decode throughput of the Dodilix design at layer sizes of a real model, beside Fuzelorn (the closest
+    existing model: a windowed attention with float32 weights beside a recurrence with a float32 state in every layer,
+    routed experts in groups with a gated shared one) at equal width and depth, and the design's own kernels one by
+    one.  One JSON line.  Random weights, synthetic token ids; CUDA events; the L2 is flushed between timed steps."""
+    import torch
+    pk = peaks()
+    l2 = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda:0")
+    clocks = ClockSampler(0)
+    clocks.start()
+    results = []
+    for width, layers in ((1024, 16), (2048, 16)):
+        row = {"width": width, "layers": layers}
+        for arm, cfg in {"dodilix": dodilix_config(width, layers), "fuzelorn": fuzelorn_config(width, layers)}.items():
+            eng = design_arm(arm, cfg, row, args, l2)
+            if not args.no_kernels:
+                row[arm + "_kernels"] = (dodilix_kernel_times if arm == "dodilix" else fuzelorn_kernel_times)(eng, l2, pk)
+            del eng
+            torch.cuda.empty_cache()
+        results.append(row)
+    time.sleep(0.06)
+    clocks.stop()
+    print(json.dumps({"workload": "dodilix", "what": "Dodilix beside Fuzelorn at equal width and depth: prefill of 2,048 "
+                      "tokens, decode at batch 8 and 1 after 2,048 tokens; each design's own kernels alone",
+                      "results": results, "dtype": "bf16", "data": "synthetic token ids, random-init weights", "peaks": pk,
+                      "clocks": clocks.summary(), "impl": "ours"}))
+
+
+def dodilix_kernel_times(eng, l2, pk):
+    """The design's own kernels alone, through the parts' own launch plans (CUDA events around the launches, L2 flushed
+    before, median of 7), for a 2,048-token portion and for 8 single tokens after 2,048: microseconds, the bytes each
+    must move with the fraction of the measured copy bandwidth, and for the recurrence and the attention cores the
+    multiply-adds they must do as TFLOP/s."""
+    import torch
+    from neurogrid_b200.csrc import ops
+    from neurogrid_b200.parts import PagedView, StepContext
+    from neurogrid_b200.parts.base import Workspace
+    model, dev = eng.model, eng.device
+    D, S = model.spec.hidden, model.spec.streams
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(3)
+    rnd = lambda *s: torch.randn(*s, generator=g, device=dev).to(torch.bfloat16)
+
+    def timed(fn):
+        ts = []
+        for _ in range(9):
+            flush_l2(l2)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        return median(ts[2:])
+
+    out = {"unit": "us"}
+    bw = pk["hbm_gbs"] * 1e9
+
+    def mem(name, us, nbytes, flops=0):
+        out[name] = {"us": round(us, 2), "bytes": int(nbytes), "of_copy_bandwidth": round(nbytes / (us * 1e-6) / bw, 3)}
+        if flops:
+            out[name]["flops"] = int(flops)
+            out[name]["tflops"] = round(flops / (us * 1e-6) / 1e12, 2)
+
+    par = next(b for b in model.blocks if type(b.mixer).__name__ == "SideBySide" and type(b.ffn).__name__ == "MoE")
+    lat = next(b.mixer for b in model.blocks if type(b.mixer).__name__ == "LatentAttention" and b.mixer.owns_cache)
+    side, f = par.mixer, par.ffn
+    left, right = side.left, side.right
+    ls, rs, ts_ = left.spec, right.spec, lat.spec
+    need = left.cache_need()
+    ps, n_pages = 16, 8 * 4096 // 16
+    kp, vp = rnd(n_pages, need.n_kv_heads, ps, need.head_dim), rnd(n_pages, need.value_shape()[0], ps, need.value_shape()[1])
+    lp = rnd(n_pages, 1, ps, lat.rank_p)
+    for rows, entries in ((PREFILL_TOKENS, 1), (8, 8)):
+        tag = "prefill2048" if entries == 1 else "decode8"
+        q_len = rows // entries
+        before = 0 if entries == 1 else 2048
+        table = torch.arange(entries * 256, dtype=torch.int32, device=dev).view(entries, 256)
+        ctx = StepContext(n_rows=rows, n_entries=entries, max_q=q_len, tokens=i32([0] * rows),
+                          positions=i32([before + t for e in range(entries) for t in range(q_len)]),
+                          row_entry=i32([e for e in range(entries) for _ in range(q_len)]),
+                          cu_q=i32([q_len * e for e in range(entries + 1)]), ctx_before=i32([before] * entries),
+                          slots=i32(list(range(entries))), status=torch.zeros(1, dtype=torch.int32, device=dev),
+                          ws=Workspace(4096, dev), dtype=torch.bfloat16, q_lens=[q_len] * entries,
+                          ctx_lens=[before] * entries, slot_ids=list(range(entries)))
+        # between two sublayers: the copies' update, the read-out and its norm
+        X, y = torch.randn(rows, S * D, generator=g, device=dev), rnd(rows, D)
+        w_in, w_out, mix = par.hc["hc1"]
+        normed = torch.empty(rows, D, dtype=torch.bfloat16, device=dev)
+        us = timed(lambda: ops.hc_step(X, S, delta=y, mix=mix, out_w=w_out, in_w=w_in, norm_w=par.mixer_norm.weight, out=normed,
+                                       eps=1e-5))
+        mem(f"{tag}_stream_copies", us, rows * D * (2 * 4 * S + 2 + 2))
+        # left: rotation, norms, page write; the attention core; the output gate
+        d, dv, H = ls.key_dim, ls.value_dim, ls.n_heads
+        vh = need.value_shape()[0]
+        qkv = rnd(rows, left.w_qkv.shape[0])
+        qb = torch.empty(rows, H * d, dtype=torch.bfloat16, device=dev)
+        pa = left.position.kernel_args()
+        view = PagedView(kp, vp, table)
+        o = torch.empty(rows, H * dv, dtype=torch.bfloat16, device=dev)
+        prep = lambda: ops.qkv_prep(qkv, qb, None, None, pa.inv_freq, kp, vp, table, ctx.positions, ctx.row_entry, H,
+                                    need.n_kv_heads, vh, d, dv, ls.eps, ctx.status, half_pairing=True, unit_norm=True)
+        core = lambda: left.attend(qb, view, ctx, o, None)
+        prep()
+        core()
+        torch.cuda.synchronize()
+        mem(f"{tag}_attention_prep", timed(prep), 2 * (H + need.n_kv_heads) * d * rows * 2 + 2 * vh * dv * rows * 2)
+        chunk = ls.chunk
+        pairs = sum(t % chunk + 1 for t in range(rows)) if entries == 1 else rows * (before % chunk + 1)
+        keys = min(before % chunk + q_len, chunk)
+        kv_bytes = entries * keys * need.elements_per_token() * 2
+        us = timed(core)
+        mem(f"{tag}_attention_core", us, kv_bytes + 2 * rows * H * d * 2, 2 * pairs * H * (d + dv))
+        out[f"{tag}_attention_core"]["of_tensor_peak"] = round(2 * pairs * H * (d + dv) / (us * 1e-6) / 1e12 / pk["bf16_tflops"], 4)
+        gate = qkv[:, qkv.shape[1] - H * dv:]
+        mem(f"{tag}_output_gate", timed(lambda: ops.gate_mul(o, gate, "sigmoid", 0.8)), 3 * rows * H * dv * 2)
+        # right: the recurrence with its decay, head norm and gate (one call of the part's launcher)
+        nH, dk, dvr = rs.n_heads, rs.key_dim, rs.value_dim
+        p, z = rnd(rows, right.w_in.shape[0]), rnd(rows, nH * dk)
+        state = torch.zeros(8, nH, dk, dvr, device=dev)
+        og = torch.empty(rows, nH * dvr, dtype=torch.bfloat16, device=dev)
+        scratch = states = None         # as the part chooses: long portions chunk by chunk, single tokens one by one
+        if right._chunked(ctx):
+            scratch = torch.empty(rows, nH * dvr, device=dev)
+            states = torch.empty(ops.gated_linear_chunked_scratch(rows, entries, nH, dk, dvr), device=dev)
+        run = lambda: ops.gated_linear(p, z, right.norm, state, og, ctx.cu_q, ctx.ctx_before, ctx.slots, entries, nH, dk, dvr,
+                                       rs.tau, rs.eps, 1.1, scratch=scratch, state_scratch=states, max_q=q_len)
+        run()
+        torch.cuda.synchronize()
+        nbytes = (p.numel() + z.numel() + og.numel()) * 2 + 2 * entries * state[0].numel() * 4
+        mem(f"{tag}_gated_linear", timed(run), nbytes, 4 * rows * nH * dk * dvr)
+        # latent attention: the row kernel, the rotation of q, the core, the heads' expansion with the gate
+        Hl, rp = ts_.n_heads, lat.rank_p
+        down = rnd(rows, lat.w_down.shape[0])
+        cq, gl = torch.empty(rows, ts_.q_rank, dtype=torch.bfloat16, device=dev), torch.empty(rows, lat.n_gate, device=dev)
+        la = lat.position.kernel_args()
+        us = timed(lambda: ops.latent_prep(down, lat.dq_norm, lat.dkv_norm, cq, lp, gl, table, ctx.positions, ctx.row_entry,
+                                           lat.n_gate, ts_.eps, ctx.status, rot=lat.rope, inv_freq=la.inv_freq))
+        mem(f"{tag}_latent_prep", us, down.numel() * 2 + cq.numel() * 2 + rows * rp * 2 + gl.numel() * 4)
+        ql, ol = rnd(rows, Hl * rp), torch.empty(rows, Hl * rp, dtype=torch.bfloat16, device=dev)
+        mem(f"{tag}_latent_rope_q", timed(lambda: ops.latent_rope_q(ql, ctx.positions, ctx.row_entry, la.inv_freq, Hl, ts_.kv_rank)),
+            2 * rows * Hl * lat.rope * 2)
+        if entries == 1:
+            corel = lambda: ops.latent_core_mma(ql, lp, table, ctx.positions, ctx.row_entry, None, ol, Hl, None, ts_.softmax_scale)
+        else:
+            n_splits = max(1, min(lat.MAX_SPLITS, 128 // rows, (before + 1) // 64))
+            part = torch.empty(max(1, ops.latent_core_partial_floats(rows, Hl, rp, n_splits)), device=dev)
+            corel = lambda: ops.latent_core(ql, lp, table, ctx.positions, ctx.row_entry, None, ol, Hl, None, ts_.softmax_scale,
+                                            n_splits, part)
+        corel()
+        torch.cuda.synchronize()
+        pairs = sum(t + 1 for t in range(rows)) if entries == 1 else rows * (before + 1)
+        us = timed(corel)
+        mem(f"{tag}_latent_core", us, entries * (before + q_len) * rp * 2 + 2 * rows * Hl * rp * 2, 4 * pairs * Hl * rp)
+        out[f"{tag}_latent_core"]["of_tensor_peak"] = round(4 * pairs * Hl * rp / (us * 1e-6) / 1e12 / pk["bf16_tflops"], 4)
+        heads_out = torch.empty(rows, Hl * ts_.value_dim, dtype=torch.bfloat16, device=dev)
+        us = timed(lambda: ops.head_up_gate(ol, lat.w_uv, gl, heads_out))
+        mem(f"{tag}_heads_expanded", us, ol.numel() * 2 + lat.w_uv.numel() * 2 + gl.numel() * 4 + heads_out.numel() * 2,
+            2 * rows * Hl * ts_.value_dim * ts_.kv_rank)
+        # router and the activation with the routing weights
+        fs = f.spec
+        xs, wts = rnd(rows, D), torch.empty(rows, fs.n_experts + 1, device=dev)
+        us = timed(lambda: ops.moe_router_sigmoid(xs, f.w_router, None, f.w_shared_gate, wts, fs.top_k, fs.n_groups,
+                                                  fs.keep_groups, softmax_scores=True, group_max=True, route_scale=fs.route_scale))
+        mem(f"{tag}_moe_router", us, rows * D * 2 + f.w_router.numel() * 4 + wts.numel() * 4)
+        gu, act = rnd(rows, 2 * f.width), torch.empty(rows, f.width, dtype=torch.bfloat16, device=dev)
+        us = timed(lambda: ops.moe_swiglu_scaled(gu, wts, act, fs.expert_ff, shared_gated=True))
+        mem(f"{tag}_moe_activation", us, 3 * rows * f.width * 2)
+    return out
+
+
 def run_reference(args):
     """The reference's own library through its stock entry points; same metric, same line."""
     shape_name = SHAPE_NAMES[args.shape]
@@ -1174,7 +1376,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=0,
                     help="tokens each request holds before decoding (default 2,048; the context is twice this)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="", choices=["", "mixed350m", "long700m", "metanex", "rofulorn", "fuzelorn"],
+    ap.add_argument("--workload", default="", choices=["", "mixed350m", "long700m", "metanex", "rofulorn", "fuzelorn", "dodilix"],
                     help="run another workload of the benchmark set through Engine.generate instead; metanex / rofulorn: "
                          "that design beside LFM2 at equal width and depth, prefill and decode, and its kernels alone")
     ap.add_argument("--repeat", type=int, default=2, help="--workload: runs (the first also warms up and captures graphs)")
@@ -1193,6 +1395,9 @@ def main():
         args.warmup = 3
     if args.workload == "metanex":
         run_metanex(args)
+        return 0
+    if args.workload == "dodilix":
+        run_dodilix(args)
         return 0
     if args.workload == "fuzelorn":
         run_fuzelorn(args)

@@ -146,3 +146,262 @@ NG_EXPORT int ng_gated_linear(const void* x, const void* z, const float* norm_w,
     }
     return ng_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------- portions, chunk by chunk
+#define GC 32
+#define GC_THREADS 256
+
+// Bs[t][i] = sum of log alpha over the chunk's tokens 0..t (rows past n repeat b_n): every thread forms its share of
+// the logarithms, then a thread per key channel adds them up along the chunk.  Ends with a barrier.
+template <typename T>
+__device__ __forceinline__ void gl_cumsum(const T* __restrict__ z, size_t ldz, size_t off, int row0, int n, int dk,
+                                          float inv_tau, float* Bs) {
+    for (int idx = threadIdx.x; idx < GC * dk; idx += GC_THREADS) {
+        const int t = idx / dk, i = idx - t * dk;
+        Bs[idx] = t < n ? gl_log_alpha(ng_ld(z + (size_t)(row0 + t) * ldz + off + i), inv_tau) : 0.f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < dk; i += GC_THREADS) {
+        float b = 0.f;
+#pragma unroll 8
+        for (int t = 0; t < GC; ++t) {
+            b += Bs[t * dk + i];
+            Bs[t * dk + i] = b;
+        }
+    }
+    __syncthreads();
+}
+
+struct GlGeom {
+    int nH, dk, dv, per_slot;        // per_slot = dk * dv + dk: a chunk's U (later the state before it) and its whole decay
+    float inv_tau;
+};
+
+// what a chunk adds to the state, U = sum_s (exp(b_n - b_s) k_s) v_s^T, and exp(b_n) behind it
+template <typename T>
+__global__ void __launch_bounds__(GC_THREADS)
+gl_chunk_local_kernel(const T* __restrict__ x, const T* __restrict__ z, float* __restrict__ scratch,
+                      const int* __restrict__ cu_q, GlGeom g) {
+    extern __shared__ float sm[];
+    const int dk = g.dk, dv = g.dv;
+    float* Bs = sm;                   // [GC][dk]
+    float* Ks = Bs + GC * dk;         // [GC][dk]
+    float* Vs = Ks + GC * dk;         // [GC][dv]
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int c = blockIdx.x, e = blockIdx.y, head = blockIdx.z;
+    const int q0 = cu_q[e], qlen = cu_q[e + 1] - q0;
+    if (c * GC >= qlen) return;
+    const int n = min(GC, qlen - c * GC), row0 = q0 + c * GC;
+    float* U = scratch + ((size_t)(q0 / GC + e + c) * g.nH + head) * g.per_slot;
+    const size_t ld = 2 * (size_t)g.nH * (dk + dv), ldz = (size_t)g.nH * dk;
+    const size_t off_q = (size_t)head * dk, off_k = (size_t)g.nH * dk + off_q;
+    const size_t off_v = 2 * (size_t)g.nH * dk + (size_t)head * dv;
+    gl_cumsum(z, ldz, off_q, row0, n, dk, g.inv_tau, Bs);
+    for (int idx = threadIdx.x; idx < GC * dk; idx += GC_THREADS) {
+        const int s = idx / dk, i = idx - s * dk;
+        Ks[idx] = s < n ? expf(Bs[(n - 1) * dk + i] - Bs[idx]) * ng_ld(x + (size_t)(row0 + s) * ld + off_k + i) : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < GC * dv; idx += GC_THREADS) {
+        const int s = idx / dv, j = idx - s * dv;
+        Vs[idx] = s < n ? ng_ld(x + (size_t)(row0 + s) * ld + off_v + j) : 0.f;
+    }
+    __syncthreads();
+    const int tj_n = dv / 4;
+    for (int tile = threadIdx.x; tile < (dk / 4) * tj_n; tile += GC_THREADS) {
+        const int ti = tile / tj_n, tj = tile - ti * tj_n;
+        float acc[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < GC; ++s) {
+            const float4 kv = *reinterpret_cast<const float4*>(Ks + s * dk + 4 * ti);
+            const float4 vv = *reinterpret_cast<const float4*>(Vs + s * dv + 4 * tj);
+            const float ka[4] = {kv.x, kv.y, kv.z, kv.w}, va[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(ka[a], va[b], acc[a][b]);
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+            *reinterpret_cast<float4*>(U + (size_t)(4 * ti + a) * dv + 4 * tj) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+    }
+    for (int i = threadIdx.x; i < dk; i += GC_THREADS) U[(size_t)dk * dv + i] = expf(Bs[(n - 1) * dk + i]);
+}
+
+// a request's chunks in order, a thread per state element: each chunk's place receives the state before it
+__global__ void __launch_bounds__(GC_THREADS)
+gl_chunk_scan_kernel(float* __restrict__ scratch, float* __restrict__ state, const int* __restrict__ cu_q,
+                     const int* __restrict__ ctx_before, const int* __restrict__ slots, GlGeom g) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int e = blockIdx.y, head = blockIdx.z;
+    const int idx = blockIdx.x * GC_THREADS + threadIdx.x;
+    const int q0 = cu_q[e], qlen = cu_q[e + 1] - q0;
+    if (qlen <= 0 || idx >= g.dk * g.dv) return;
+    const int chunks = (qlen + GC - 1) / GC, i = idx / g.dv;
+    float* S = state + ((size_t)slots[e] * g.nH + head) * g.dk * g.dv;
+    float* U = ng_after_wait(scratch) + ((size_t)(q0 / GC + e) * g.nH + head) * g.per_slot;
+    float s = ctx_before[e] > 0 ? S[idx] : 0.f;
+    for (int c = 0; c < chunks; ++c, U += (size_t)g.nH * g.per_slot) {
+        const float u = U[idx], d = U[(size_t)g.dk * g.dv + i];
+        U[idx] = s;
+        s = fmaf(d, s, u);
+    }
+    S[idx] = s;
+}
+
+// o_t = sum_(s<=t) A[t][s] v_s + S^T (q_t exp(b_t)) of every chunk, S the state before it; float32 into `raw`
+template <typename T>
+__global__ void __launch_bounds__(GC_THREADS)
+gl_chunk_out_kernel(const T* __restrict__ x, const T* __restrict__ z, const float* __restrict__ scratch,
+                    float* __restrict__ raw, const int* __restrict__ cu_q, GlGeom g) {
+    extern __shared__ float sm[];
+    const int dk = g.dk, dv = g.dv;
+    float* Bs = sm;                   // [GC][dk]
+    float* Qs = Bs + GC * dk;         // [GC][dk]
+    float* Ks = Qs + GC * dk;         // [GC][dk]
+    float* Vs = Ks + GC * dk;         // [GC][dv]
+    float* As = Vs + GC * dv;         // [GC][GC + 1]
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int c = blockIdx.x, e = blockIdx.y, head = blockIdx.z;
+    const int q0 = cu_q[e], qlen = cu_q[e + 1] - q0;
+    if (c * GC >= qlen) return;
+    const int n = min(GC, qlen - c * GC), row0 = q0 + c * GC;
+    const float* S = ng_after_wait(scratch) + ((size_t)(q0 / GC + e + c) * g.nH + head) * g.per_slot;
+    const size_t ld = 2 * (size_t)g.nH * (dk + dv), ldz = (size_t)g.nH * dk;
+    const size_t off_q = (size_t)head * dk, off_k = (size_t)g.nH * dk + off_q;
+    const size_t off_v = 2 * (size_t)g.nH * dk + (size_t)head * dv;
+    const float qscale = rsqrtf((float)dk);
+    gl_cumsum(z, ldz, off_q, row0, n, dk, g.inv_tau, Bs);
+    for (int idx = threadIdx.x; idx < GC * dk; idx += GC_THREADS) {
+        const int t = idx / dk, i = idx - t * dk;
+        Qs[idx] = t < n ? ng_ld(x + (size_t)(row0 + t) * ld + off_q + i) * qscale : 0.f;
+        Ks[idx] = t < n ? ng_ld(x + (size_t)(row0 + t) * ld + off_k + i) : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < GC * dv; idx += GC_THREADS) {
+        const int s = idx / dv, j = idx - s * dv;
+        Vs[idx] = s < n ? ng_ld(x + (size_t)(row0 + s) * ld + off_v + j) : 0.f;
+    }
+    __syncthreads();
+    // scores inside the chunk; every exponent is a difference that is not positive
+    for (int idx = threadIdx.x; idx < GC * GC; idx += GC_THREADS) {
+        const int t = idx / GC, s = idx - t * GC;
+        float a = 0.f;
+        if (s <= t && t < n) {
+            const float *qt = Qs + t * dk, *ks = Ks + s * dk, *bt = Bs + t * dk, *bs = Bs + s * dk;
+            float a0 = 0.f, a1 = 0.f;
+            for (int i = 0; i < dk; i += 2) {
+                a0 = fmaf(qt[i] * ks[i], expf(bt[i] - bs[i]), a0);
+                a1 = fmaf(qt[i + 1] * ks[i + 1], expf(bt[i + 1] - bs[i + 1]), a1);
+            }
+            a = a0 + a1;
+        }
+        As[t * (GC + 1) + s] = a;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < GC * dk; idx += GC_THREADS) Qs[idx] *= expf(Bs[idx]);
+    __syncthreads();
+    const int tj_n = dv / 4;
+    for (int tile = threadIdx.x; tile < (GC / 4) * tj_n; tile += GC_THREADS) {
+        const int tt = tile / tj_n, tj = tile - tt * tj_n;
+        float acc[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < GC; ++s) {
+            const float4 vv = *reinterpret_cast<const float4*>(Vs + s * dv + 4 * tj);
+            const float va[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float w = As[(4 * tt + a) * (GC + 1) + s];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(w, va[b], acc[a][b]);
+            }
+        }
+#pragma unroll 4
+        for (int i = 0; i < dk; ++i) {
+            const float4 sv = *reinterpret_cast<const float4*>(S + (size_t)i * dv + 4 * tj);
+            const float sa[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float w = Qs[(4 * tt + a) * dk + i];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(w, sa[b], acc[a][b]);
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+            if (4 * tt + a < n)
+                *reinterpret_cast<float4*>(raw + (size_t)(row0 + 4 * tt + a) * g.nH * dv + (size_t)head * dv + 4 * tj) =
+                    make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+    }
+}
+
+// each head's o over its root mean square, times the weight, silu(gate) and out_scale: a warp per (row, head)
+template <typename T>
+__global__ void gl_finish_kernel(const float* __restrict__ raw, const T* __restrict__ x, const float* __restrict__ norm_w,
+                                 T* __restrict__ out, const int* __restrict__ row_entry_or_null, int n_rows, GlGeom g, float eps,
+                                 float out_scale, int ldo) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= n_rows * g.nH) return;
+    const int row = w / g.nH, head = w - row * g.nH;
+    const float* o = ng_after_wait(raw) + (size_t)row * g.nH * g.dv + (size_t)head * g.dv;
+    const T* gate = x + (size_t)row * 2 * g.nH * (g.dk + g.dv) + 2 * (size_t)g.nH * g.dk + (size_t)g.nH * g.dv + (size_t)head * g.dv;
+    float ss = 0.f;
+    for (int j = lane; j < g.dv; j += 32) ss = fmaf(o[j], o[j], ss);
+    const float r = rsqrtf(ng_warp_sum(ss) / (float)g.dv + eps);
+    for (int j = lane; j < g.dv; j += 32) {
+        const float gt = ng_ld(gate + j);
+        ng_st(out + (size_t)row * ldo + (size_t)head * g.dv + j, o[j] * r * norm_w[j] * (gt / (1.f + expf(-gt))) * out_scale);
+    }
+}
+
+static size_t gl_out_smem(int dk, int dv) { return ((size_t)3 * GC * dk + (size_t)GC * dv + GC * (GC + 1)) * sizeof(float); }
+
+// whether the chunk-by-chunk kernels take the head sizes: rows and columns in fours, the tiles within shared memory
+NG_EXPORT int ng_gated_linear_chunked_takes(int dk, int dv) {
+    return dk > 0 && dv > 0 && dk % 4 == 0 && dv % 4 == 0 && gl_out_smem(dk, dv) <= 160 * 1024;
+}
+
+// raw: float32 [n_rows, nH * dv]; scratch: (n_rows / GC + n_entries + 1) * nH * (dk * dv + dk) float32 values
+NG_EXPORT int ng_gated_linear_chunked(const void* x, const void* z, const float* norm_w, float* state, void* out,
+                                      float* raw, float* scratch, const int* cu_q, const int* ctx_before, const int* slots,
+                                      int n_entries, int n_rows, int max_q, int nH, int dk, int dv, float tau, float eps,
+                                      float out_scale, int ldo, int act_bf16, cudaStream_t stream) {
+    if (n_entries <= 0 || n_rows <= 0) return NG_OK;
+    if (nH <= 0 || nH > 65535 || n_entries > 65535 || max_q <= 0 || !(tau > 0.f) || ldo < nH * dv ||
+        !ng_gated_linear_chunked_takes(dk, dv) || !raw || !scratch)
+        return NG_BAD_SIZE;
+    const GlGeom g{nH, dk, dv, dk * dv + dk, 1.f / tau};
+    const int chunks = (max_q + GC - 1) / GC;
+    const dim3 grid(chunks, n_entries, nH), sgrid((dk * dv + GC_THREADS - 1) / GC_THREADS, n_entries, nH);
+    const size_t smem_local = ((size_t)2 * GC * dk + (size_t)GC * dv) * sizeof(float), smem_out = gl_out_smem(dk, dv);
+    const unsigned fblocks = (unsigned)(((size_t)n_rows * nH + 7) / 8);
+#define GL_CHUNKED(TT)                                                                                                 \
+    {                                                                                                                  \
+        static bool configured = false;                                                                                \
+        if (!configured) {                                                                                             \
+            if (cudaFuncSetAttribute(gl_chunk_local_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess || \
+                cudaFuncSetAttribute(gl_chunk_out_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)     \
+                return NG_LAUNCH_FAILED;                                                                               \
+            configured = true;                                                                                         \
+        }                                                                                                              \
+        NG_LAUNCH((gl_chunk_local_kernel<TT>), grid, GC_THREADS, smem_local, stream, (const TT*)x, (const TT*)z, scratch, cu_q, g); \
+        NG_LAUNCH((gl_chunk_scan_kernel), sgrid, GC_THREADS, 0, stream, scratch, state, cu_q, ctx_before, slots, g);   \
+        NG_LAUNCH((gl_chunk_out_kernel<TT>), grid, GC_THREADS, smem_out, stream, (const TT*)x, (const TT*)z,           \
+                  (const float*)scratch, raw, cu_q, g);                                                                \
+        NG_LAUNCH((gl_finish_kernel<TT>), fblocks, 256, 0, stream, (const float*)raw, (const TT*)x, norm_w, (TT*)out,  \
+                  (const int*)nullptr, n_rows, g, eps, out_scale, ldo);                                                \
+    }
+    if (act_bf16) GL_CHUNKED(__nv_bfloat16) else GL_CHUNKED(float)
+    return ng_launch_status();
+}

@@ -96,7 +96,8 @@ __global__ void latent_rope_q_kernel(T* __restrict__ q, const int* __restrict__ 
 
 // A block takes HU_ROWS rows of one head: their weighted latents lie in shared memory (float32), a warp takes output
 // columns in turn with its lanes dealt over the latent's coordinates, so W[h] is read once per HU_ROWS rows, in order.
-// A (row, column) sum is formed the same way whatever else the step holds.
+// A (row, column) sum is formed the same way whatever else the step holds.  A step of few rows deals a head's output
+// columns to gridDim.z blocks, so that the weights are streamed by many blocks.
 #define HU_ROWS 16
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -114,7 +115,7 @@ head_up_gate_kernel(const T* __restrict__ o, const T* __restrict__ w, const floa
     }
     __syncthreads();
     const T* wh = w + (size_t)head * dv * rank;
-    for (int v = warp; v < dv; v += nwarp) {
+    for (int v = blockIdx.z * nwarp + warp; v < dv; v += nwarp * gridDim.z) {
         float acc[HU_ROWS];
 #pragma unroll
         for (int r = 0; r < HU_ROWS; ++r) acc[r] = 0.f;
@@ -418,7 +419,9 @@ NG_EXPORT int ng_head_up_gate(const void* o, const void* w, const float* gate, v
     if (nH <= 0 || nH > 65535 || rank <= 0 || rank > rp || dv <= 0 || ldo < nH * dv) return NG_BAD_SIZE;
     const size_t smem = (size_t)HU_ROWS * rank * sizeof(float);
     if (smem > 160 * 1024) return NG_BAD_SIZE;
-    dim3 grid((n_rows + HU_ROWS - 1) / HU_ROWS, nH);
+    const int tiles = (n_rows + HU_ROWS - 1) / HU_ROWS;
+    const int slices = tiles * nH >= 256 ? 1 : max(1, min((dv + 7) / 8, 256 / (tiles * nH)));
+    dim3 grid(tiles, nH, slices);
 #define HU_LAUNCH(TT)                                                                                                  \
     {                                                                                                                  \
         static bool configured = false;                                                                                \

@@ -947,7 +947,8 @@ def gated_linear_chunked_scratch(n_rows: int, n_entries: int, n_heads: int, key_
 
 def gated_linear_chunked_takes(key_dim: int, value_dim: int) -> bool:
     """Whether the chunk-by-chunk kernels take the head sizes."""
-    return False
+    f = _fn("gated_linear", "ng_gated_linear_chunked_takes", [_c_int, _c_int])
+    return bool(f(int(key_dim), int(value_dim)))
 
 
 def scale_(x: torch.Tensor, factor: float) -> None:
