@@ -606,6 +606,7 @@ def design_arm(arm, cfg, row, args, l2):
     eng = Engine(config=cfg, random_weights=0, dtype="bf16", max_seq_len=8192, max_requests=8,
                  max_tokens_per_step=2048, num_pages=8 * 4096 // 16)
     r = eng.runner
+    r.keep_graphs = True            # for the count of kernel nodes in the decode graph
     V = eng.model.spec.vocab_size
     g = torch.Generator().manual_seed(1)
     toks = lambda n: torch.randint(0, V, (n,), generator=g).tolist()
@@ -650,6 +651,7 @@ def design_arm(arm, cfg, row, args, l2):
         row[f"{arm}_decode{batch}_tok_s"] = round(batch / ms * 1e3)
     r.check_status()
     row[arm + "_weights_gb"] = round(eng.model.weight_bytes() / 1e9, 3)
+    row[arm + "_decode_launches"] = max((n for k, n in r.graph_kernel_nodes().items() if k[0] != "portion"), default=0)
     return eng
 
 

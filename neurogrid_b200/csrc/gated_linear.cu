@@ -152,21 +152,21 @@ NG_EXPORT int ng_gated_linear(const void* x, const void* z, const float* norm_w,
 #define GC_THREADS 256
 
 // Bs[t][i] = sum of log alpha over the chunk's tokens 0..t (rows past n repeat b_n): every thread forms its share of
-// the logarithms, then a thread per key channel adds them up along the chunk.  Ends with a barrier.
+// the logarithms, then a thread per key channel adds them up along the chunk.  Rows of Bs lie ldb apart.  Ends with a barrier.
 template <typename T>
 __device__ __forceinline__ void gl_cumsum(const T* __restrict__ z, size_t ldz, size_t off, int row0, int n, int dk,
-                                          float inv_tau, float* Bs) {
+                                          float inv_tau, float* Bs, int ldb) {
     for (int idx = threadIdx.x; idx < GC * dk; idx += GC_THREADS) {
         const int t = idx / dk, i = idx - t * dk;
-        Bs[idx] = t < n ? gl_log_alpha(ng_ld(z + (size_t)(row0 + t) * ldz + off + i), inv_tau) : 0.f;
+        Bs[t * ldb + i] = t < n ? gl_log_alpha(ng_ld(z + (size_t)(row0 + t) * ldz + off + i), inv_tau) : 0.f;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < dk; i += GC_THREADS) {
         float b = 0.f;
 #pragma unroll 8
         for (int t = 0; t < GC; ++t) {
-            b += Bs[t * dk + i];
-            Bs[t * dk + i] = b;
+            b += Bs[t * ldb + i];
+            Bs[t * ldb + i] = b;
         }
     }
     __syncthreads();
@@ -197,7 +197,7 @@ gl_chunk_local_kernel(const T* __restrict__ x, const T* __restrict__ z, float* _
     const size_t ld = 2 * (size_t)g.nH * (dk + dv), ldz = (size_t)g.nH * dk;
     const size_t off_q = (size_t)head * dk, off_k = (size_t)g.nH * dk + off_q;
     const size_t off_v = 2 * (size_t)g.nH * dk + (size_t)head * dv;
-    gl_cumsum(z, ldz, off_q, row0, n, dk, g.inv_tau, Bs);
+    gl_cumsum(z, ldz, off_q, row0, n, dk, g.inv_tau, Bs, dk);
     for (int idx = threadIdx.x; idx < GC * dk; idx += GC_THREADS) {
         const int s = idx / dk, i = idx - s * dk;
         Ks[idx] = s < n ? expf(Bs[(n - 1) * dk + i] - Bs[idx]) * ng_ld(x + (size_t)(row0 + s) * ld + off_k + i) : 0.f;
@@ -261,10 +261,11 @@ gl_chunk_out_kernel(const T* __restrict__ x, const T* __restrict__ z, const floa
                     float* __restrict__ raw, const int* __restrict__ cu_q, GlGeom g) {
     extern __shared__ float sm[];
     const int dk = g.dk, dv = g.dv;
-    float* Bs = sm;                   // [GC][dk]
-    float* Qs = Bs + GC * dk;         // [GC][dk]
-    float* Ks = Qs + GC * dk;         // [GC][dk]
-    float* Vs = Ks + GC * dk;         // [GC][dv]
+    const int ldk = dk + 1;           // a row's pitch: the scores walk rows with a lane per row, a pitch of dk would put them in one bank
+    float* Bs = sm;                   // [GC][ldk]
+    float* Qs = Bs + GC * ldk;        // [GC][ldk]
+    float* Ks = Qs + GC * ldk;        // [GC][ldk]
+    float* Vs = Ks + GC * ldk + (4 - (3 * GC * ldk) % 4) % 4;      // [GC][dv], 16-byte aligned
     float* As = Vs + GC * dv;         // [GC][GC + 1]
     ng_pdl_trigger();
     ng_pdl_wait();
@@ -277,11 +278,11 @@ gl_chunk_out_kernel(const T* __restrict__ x, const T* __restrict__ z, const floa
     const size_t off_q = (size_t)head * dk, off_k = (size_t)g.nH * dk + off_q;
     const size_t off_v = 2 * (size_t)g.nH * dk + (size_t)head * dv;
     const float qscale = rsqrtf((float)dk);
-    gl_cumsum(z, ldz, off_q, row0, n, dk, g.inv_tau, Bs);
+    gl_cumsum(z, ldz, off_q, row0, n, dk, g.inv_tau, Bs, ldk);
     for (int idx = threadIdx.x; idx < GC * dk; idx += GC_THREADS) {
         const int t = idx / dk, i = idx - t * dk;
-        Qs[idx] = t < n ? ng_ld(x + (size_t)(row0 + t) * ld + off_q + i) * qscale : 0.f;
-        Ks[idx] = t < n ? ng_ld(x + (size_t)(row0 + t) * ld + off_k + i) : 0.f;
+        Qs[t * ldk + i] = t < n ? ng_ld(x + (size_t)(row0 + t) * ld + off_q + i) * qscale : 0.f;
+        Ks[t * ldk + i] = t < n ? ng_ld(x + (size_t)(row0 + t) * ld + off_k + i) : 0.f;
     }
     for (int idx = threadIdx.x; idx < GC * dv; idx += GC_THREADS) {
         const int s = idx / dv, j = idx - s * dv;
@@ -293,18 +294,21 @@ gl_chunk_out_kernel(const T* __restrict__ x, const T* __restrict__ z, const floa
         const int t = idx / GC, s = idx - t * GC;
         float a = 0.f;
         if (s <= t && t < n) {
-            const float *qt = Qs + t * dk, *ks = Ks + s * dk, *bt = Bs + t * dk, *bs = Bs + s * dk;
+            const float *qt = Qs + t * ldk, *ks = Ks + s * ldk, *bt = Bs + t * ldk, *bs = Bs + s * ldk;
             float a0 = 0.f, a1 = 0.f;
             for (int i = 0; i < dk; i += 2) {
-                a0 = fmaf(qt[i] * ks[i], expf(bt[i] - bs[i]), a0);
-                a1 = fmaf(qt[i + 1] * ks[i + 1], expf(bt[i + 1] - bs[i + 1]), a1);
+                a0 = fmaf(qt[i] * ks[i], __expf(bt[i] - bs[i]), a0);
+                a1 = fmaf(qt[i + 1] * ks[i + 1], __expf(bt[i + 1] - bs[i + 1]), a1);
             }
             a = a0 + a1;
         }
         As[t * (GC + 1) + s] = a;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < GC * dk; idx += GC_THREADS) Qs[idx] *= expf(Bs[idx]);
+    for (int idx = threadIdx.x; idx < GC * dk; idx += GC_THREADS) {
+        const int t = idx / dk, i = idx - t * dk;
+        Qs[t * ldk + i] *= expf(Bs[t * ldk + i]);
+    }
     __syncthreads();
     const int tj_n = dv / 4;
     for (int tile = threadIdx.x; tile < (GC / 4) * tj_n; tile += GC_THREADS) {
@@ -331,7 +335,7 @@ gl_chunk_out_kernel(const T* __restrict__ x, const T* __restrict__ z, const floa
             const float sa[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
-                const float w = Qs[(4 * tt + a) * dk + i];
+                const float w = Qs[(4 * tt + a) * (dk + 1) + i];
 #pragma unroll
                 for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(w, sa[b], acc[a][b]);
             }
@@ -365,7 +369,7 @@ __global__ void gl_finish_kernel(const float* __restrict__ raw, const T* __restr
     }
 }
 
-static size_t gl_out_smem(int dk, int dv) { return ((size_t)3 * GC * dk + (size_t)GC * dv + GC * (GC + 1)) * sizeof(float); }
+static size_t gl_out_smem(int dk, int dv) { return ((size_t)3 * GC * (dk + 1) + 4 + (size_t)GC * dv + GC * (GC + 1)) * sizeof(float); }
 
 // whether the chunk-by-chunk kernels take the head sizes: rows and columns in fours, the tiles within shared memory
 NG_EXPORT int ng_gated_linear_chunked_takes(int dk, int dv) {
