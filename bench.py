@@ -1126,11 +1126,11 @@ def dodilix_config(width, layers):
     heads = width // 128
     left = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
             "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": 64}}
-    right = {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 64}
-    parallel = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.8, "right_scale": 1.1}}
+    right = {"heads": heads, "dim": 128, "vdim": 128, "tau": 8.0, "decay_rank": 64}
+    parallel = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.9, "right_scale": 1.2}}
     latent = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": width // 2, "kv_rank": 192,
               "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
-    moe = {"kind": "moe", "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 4, "scale": 2.0, "groups": {"count": 4, "keep": 2}},
            "expert": {"ff": width // 4}, "shared": {"ff": width // 2}}
     dense = {"kind": "dense", "ff": 4 * width}
     out = []
@@ -1142,7 +1142,7 @@ def dodilix_config(width, layers):
         layer["mlp"] = dense if i == 0 else moe
         out.append(layer)
     return {"architecture": "Dodilix", "vocab": 65536, "width": width, "streams": 4, "norm": {"eps": 1e-5},
-            "logit_scale": 0.25, "embedding": {"scale": 2.0}, "layers": out}
+            "logit_scale": 0.5, "embedding": {"scale": 2.0}, "layers": out}
 
 
 def run_dodilix(args):
@@ -1260,7 +1260,7 @@ def dodilix_kernel_times(eng, l2, pk):
         mem(f"{tag}_attention_core", us, kv_bytes + 2 * rows * H * d * 2, 2 * pairs * H * (d + dv))
         out[f"{tag}_attention_core"]["of_tensor_peak"] = round(2 * pairs * H * (d + dv) / (us * 1e-6) / 1e12 / pk["bf16_tflops"], 4)
         gate = qkv[:, qkv.shape[1] - H * dv:]
-        mem(f"{tag}_output_gate", timed(lambda: ops.gate_mul(o, gate, "sigmoid", 0.8)), 3 * rows * H * dv * 2)
+        mem(f"{tag}_output_gate", timed(lambda: ops.gate_mul(o, gate, "sigmoid", 0.9)), 3 * rows * H * dv * 2)
         # right: the recurrence with its decay, head norm and gate (one call of the part's launcher)
         nH, dk, dvr = rs.n_heads, rs.key_dim, rs.value_dim
         p, z = rnd(rows, right.w_in.shape[0]), rnd(rows, nH * dk)
@@ -1271,7 +1271,7 @@ def dodilix_kernel_times(eng, l2, pk):
             scratch = torch.empty(rows, nH * dvr, device=dev)
             states = torch.empty(ops.gated_linear_chunked_scratch(rows, entries, nH, dk, dvr), device=dev)
         run = lambda: ops.gated_linear(p, z, right.norm, state, og, ctx.cu_q, ctx.ctx_before, ctx.slots, entries, nH, dk, dvr,
-                                       rs.tau, rs.eps, 1.1, scratch=scratch, state_scratch=states, max_q=q_len)
+                                       rs.tau, rs.eps, 1.2, scratch=scratch, state_scratch=states, max_q=q_len)
         run()
         torch.cuda.synchronize()
         nbytes = (p.numel() + z.numel() + og.numel()) * 2 + 2 * entries * state[0].numel() * 4

@@ -246,10 +246,24 @@ gl_chunk_scan_kernel(float* __restrict__ scratch, float* __restrict__ state, con
     float* S = state + ((size_t)slots[e] * g.nH + head) * g.dk * g.dv;
     float* U = ng_after_wait(scratch) + ((size_t)(q0 / GC + e) * g.nH + head) * g.per_slot;
     float s = ctx_before[e] > 0 ? S[idx] : 0.f;
-    for (int c = 0; c < chunks; ++c, U += (size_t)g.nH * g.per_slot) {
-        const float u = U[idx], d = U[(size_t)g.dk * g.dv + i];
-        U[idx] = s;
-        s = fmaf(d, s, u);
+    // eight chunks' terms are requested together, then the recurrence walks them: a load per step would wait for
+    // the store before it (the compiler cannot tell the places apart)
+    const size_t step = (size_t)g.nH * g.per_slot;
+    for (int c0 = 0; c0 < chunks; c0 += 8, U += 8 * step) {
+        float u[8], d[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const bool in = c0 + k < chunks;
+            u[k] = in ? U[k * step + idx] : 0.f;
+            d[k] = in ? U[k * step + (size_t)g.dk * g.dv + i] : 1.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (c0 + k < chunks) {
+                U[k * step + idx] = s;
+                s = fmaf(d[k], s, u[k]);
+            }
+        }
     }
     S[idx] = s;
 }
@@ -329,7 +343,7 @@ gl_chunk_out_kernel(const T* __restrict__ x, const T* __restrict__ z, const floa
                 for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(w, va[b], acc[a][b]);
             }
         }
-#pragma unroll 4
+#pragma unroll 8
         for (int i = 0; i < dk; ++i) {
             const float4 sv = *reinterpret_cast<const float4*>(S + (size_t)i * dv + 4 * tj);
             const float sa[4] = {sv.x, sv.y, sv.z, sv.w};

@@ -206,16 +206,25 @@ latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ page
             lm_split3(s[2 * kk][2], s[2 * kk][3], ph[1], pm[1], pl[1]);
             lm_split3(s[2 * kk + 1][0], s[2 * kk + 1][1], ph[2], pm[2], pl[2]);
             lm_split3(s[2 * kk + 1][2], s[2 * kk + 1][3], ph[3], pm[3], pl[3]);
+            // four column tiles at a time: the three terms of one accumulator lie four instructions apart, so the
+            // tensor pipe is not held up by the chain of an accumulator's own additions
 #pragma unroll
-            for (int dt = 0; dt < LM_R / 8; dt += 2) {
-                uint32_t b[4];                                  // (dt: keys 0-7, 8-15), (dt + 1: keys 0-7, 8-15) of this step
+            for (int dt = 0; dt < LM_R / 8; dt += 4) {
+                uint32_t b[4], c[4];                            // (dt: keys 0-7, 8-15), (dt + 1: ...) and (dt + 2), (dt + 3) of this step
                 lm_ldsm4_t(b, tile + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LM_LD + (dt + (lane >> 4)) * 8);
+                lm_ldsm4_t(c, tile + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LM_LD + (dt + 2 + (lane >> 4)) * 8);
                 lm_mma(o[dt], pl, b[0], b[1]);                  // smallest terms first
-                lm_mma(o[dt], pm, b[0], b[1]);
-                lm_mma(o[dt], ph, b[0], b[1]);
                 lm_mma(o[dt + 1], pl, b[2], b[3]);
+                lm_mma(o[dt + 2], pl, c[0], c[1]);
+                lm_mma(o[dt + 3], pl, c[2], c[3]);
+                lm_mma(o[dt], pm, b[0], b[1]);
                 lm_mma(o[dt + 1], pm, b[2], b[3]);
+                lm_mma(o[dt + 2], pm, c[0], c[1]);
+                lm_mma(o[dt + 3], pm, c[2], c[3]);
+                lm_mma(o[dt], ph, b[0], b[1]);
                 lm_mma(o[dt + 1], ph, b[2], b[3]);
+                lm_mma(o[dt + 2], ph, c[0], c[1]);
+                lm_mma(o[dt + 3], ph, c[2], c[3]);
             }
         }
         __syncwarp();                                            // the tile is free for the copy after next

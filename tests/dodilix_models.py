@@ -68,7 +68,7 @@ DODI_A = {
         _latent(3, 8, 4, 6, 20, 24, 0.3, 500.0, _moe(6, 2, 16, (3, 1), 24, 1.7)),
         _parallel(_left(4, 2, 16, 12, 0.3, 13, (1000.0, 8)), _right(3, 8, 10, 7.0, 5), {"kind": "dense", "ff": 40}, (0.7, 1.3)),
         _latent(2, 12, 4, 10, 16, 24, 0.25, 500.0, None, kv_from=0),
-        _parallel(_left(6, 2, 8, 20, 0.4, 9, (50.0, 8)), _right(2, 24, 12, 3.0, 9), _moe(8, 3, 8, (2, 1), 16, 2.5), (1.2, 0.8)),
+        _parallel(_left(6, 2, 8, 20, 0.4, 9, (50.0, 8)), _right(2, 24, 12, 3.0, 9), _moe(10, 3, 8, (5, 2), 16, 2.25), (1.2, 0.85)),
     ],
 }
 
@@ -80,7 +80,7 @@ DODI_B = {
     "layers": [
         _parallel(_left(1, 1, 8, 8, 0.35, 1), _right(1, 8, 8, 1.0, 1), {"kind": "dense", "ff": 24}),
         _latent(1, 6, 0, 6, 6, 6, 0.4, 0.0, _moe(2, 1, 12)),
-        _parallel(_left(2, 2, 6, 10, 0.5, None, (10000.0, 6)), _right(2, 5, 7, 16.0, 3), _moe(3, 3, 8, (3, 3))),
+        _parallel(_left(2, 2, 6, 10, 0.5, None, (10000.0, 6)), _right(2, 5, 7, 11.0, 3), _moe(3, 3, 8, (3, 3))),
         _latent(2, 4, 6, 5, 7, 6, 0.5, 100.0, None),
     ],
 }
@@ -92,7 +92,7 @@ DODI_C = {
     "architecture": "Dodilix", "vocab": 90, "width": 64, "streams": 2, "norm": {"eps": 1e-6}, "logit_scale": 1.5,
     "embedding": {"scale": 0.75},
     "layers": [
-        _parallel(_left(4, 1, 64, 64, 0.15, 70, (10000.0, 32)), _right(2, 32, 32, 8.0, 4), _moe(4, 2, 16, (4, 3), 24, 1.0), (0.9, 1.1)),
+        _parallel(_left(4, 1, 64, 64, 0.15, 70, (10000.0, 32)), _right(2, 32, 16, 8.0, 4), _moe(4, 2, 16, (4, 3), 24, 1.0), (0.9, 1.15)),
         _latent(4, 16, 8, 16, 24, 56, 0.2, 1000.0, {"kind": "dense", "ff": 48}),
         _parallel(_left(8, 2, 32, 16, 0.2, 33, (100.0, 32)), _right(4, 16, 48, 2.0, 8), None),
         _latent(5, 8, 8, 24, 16, 56, 0.3, 1000.0, _moe(4, 1, 16, None, 16), kv_from=1),
@@ -100,8 +100,19 @@ DODI_C = {
     ],
 }
 
-CONFIGS = {"A": (DODI_A, 41), "B": (DODI_B, 42), "B0": (DODI_B0, 43), "C": (DODI_C, 44)}
-PAGE_SIZE = {"A": 8, "B": 16, "B0": 4, "C": 8}
+# D: a width that is no multiple of four, five copies, a cached row wider than the latent cores take (272 columns: the
+# plain attention kernel serves, with the gate behind it) and a reader of it, a key/value group of more heads than a tile has rows
+DODI_D = {
+    "architecture": "Dodilix", "vocab": 70, "width": 50, "streams": 5, "norm": {"eps": 1e-5}, "logit_scale": 0.8,
+    "layers": [
+        _latent(2, 10, 8, 14, 12, 264, 0.2, 300.0, {"kind": "dense", "ff": 30}),
+        _parallel(_left(34, 2, 8, 6, 0.35, 21, (10.0, 4)), _right(1, 12, 20, 4.0, 2), None, (1.0, 0.5)),
+        _latent(3, 6, 8, 9, 10, 264, 0.25, 300.0, _moe(5, 2, 10, None, None, 0.7), kv_from=0),
+    ],
+}
+
+CONFIGS = {"A": (DODI_A, 41), "B": (DODI_B, 42), "B0": (DODI_B0, 43), "C": (DODI_C, 44), "D": (DODI_D, 45)}
+PAGE_SIZE = {"A": 8, "B": 16, "B0": 4, "C": 8, "D": 8}
 
 
 def draw_weights(config: dict, seed: int, router_gain: float = 3.0, same_experts: bool = False):
