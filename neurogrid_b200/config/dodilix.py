@@ -113,9 +113,7 @@ class DodilixConfig:
                 rot_dim = _need(m, mp, "rot_dim", int, positive=False) if m.get("rot_dim") is not None else 0
                 if rot_dim < 0 or rot_dim % 2:
                     raise ConfigError(f"{mp}rot_dim = {rot_dim} must be even and not negative")
-                rot = _rot(m, mp, rot_dim)
-                if rot_dim and (rot is None or rot[1] != rot_dim):
-                    raise ConfigError(f"{mp}rot.dims must equal rot_dim = {rot_dim}: the rotated part is rotated whole")
+                _rot(m, mp, rot_dim)                    # rot.dims at most rot_dim: the part's first coordinates are rotated
                 src = m.get("kv_from")
                 if src is not None:
                     if not isinstance(src, int) or isinstance(src, bool) or not 0 <= src < i:
@@ -180,7 +178,8 @@ class DodilixConfig:
         D, m = self.width, layer["mixer"]
         if layer["type"] == "latent_attention":
             rot_dim = int(m.get("rot_dim") or 0)
-            position = RopeSpec(rot_dim, float(m["rot"]["base"]), "adjacent") if rot_dim else None
+            rot = _rot(m, f"layers[{i}].mixer.", rot_dim)
+            position = RopeSpec(rot_dim, rot[0] if rot else 1.0, "adjacent", rotary_dims=rot[1] if rot else 0) if rot_dim else None
             return LatentAttentionSpec(hidden=D, n_heads=m["heads"], key_dim=m["dim"], value_dim=m["vdim"], q_rank=m["q_rank"],
                                        kv_rank=m["kv_rank"], softmax_scale=float(m["scale"]), eps=self.norm_eps, window=None,
                                        rope_dim=rot_dim, position=position, gate="element")

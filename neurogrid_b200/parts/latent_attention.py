@@ -89,6 +89,20 @@ class LatentAttention:
     def cache_need(self):
         return PagedNeed(1, self.rank_p, self.spec.window, values=False)
 
+    def _position_args(self):
+        """The rotation of the rotated part as the row kernels take it: a frequency per pair of the part; pairs behind
+        the encoding's rotated coordinates get the frequency zero (they pass unchanged)."""
+        if getattr(self, "_pa", None) is None:
+            pa = PositionArgs.of(self.position.kernel_args())
+            if pa.pos_scale != 1.0 or (pa.half_pairing and pa.inv_freq is not None and pa.inv_freq.numel() != self.rope // 2):
+                raise NotImplementedError("the rotated part takes unscaled positions, and pairs (i, i + half) only whole")
+            f = torch.zeros(self.rope // 2, dtype=torch.float32, device=self.device)
+            if pa.inv_freq is not None:
+                f[: pa.inv_freq.numel()] = pa.inv_freq.to(self.device)
+            pa.inv_freq = f
+            self._pa = pa
+        return self._pa
+
     def kernels(self):
         jobs = [("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None), ("latent", None)]
         if ops.latent_core_mma_takes(self.spec.n_heads, self.rank_p, self.dtype):
@@ -113,9 +127,7 @@ class LatentAttention:
         ops.linear(x, w_down, None, down)
         cq = ctx.ws.buf("lat_cq", n, s.q_rank, self.dtype)
         gate = ctx.ws.buf("lat_gate", n, self.n_gate, torch.float32)
-        pa = PositionArgs.of(self.position.kernel_args()) if self.rope else None
-        if pa is not None and (pa.inv_freq is None or pa.inv_freq.numel() != self.rope // 2 or pa.pos_scale != 1.0):
-            raise NotImplementedError("the rotated key part is rotated whole, by unscaled positions")
+        pa = self._position_args() if self.rope else None
         ops.latent_prep(down, self.dq_norm, self.dkv_norm if writes else None, cq, cache.k_pages if writes else None, gate,
                         cache.table, ctx.positions, ctx.row_entry, self.n_gate, s.eps, ctx.status,
                         rot=self.rope if writes else 0, inv_freq=pa.inv_freq if pa else None,

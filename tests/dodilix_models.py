@@ -38,10 +38,10 @@ def _parallel(left, right, mlp, scales=None):
     return {"type": "parallel", "mixer": m, "mlp": mlp}
 
 
-def _latent(heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, base, mlp, kv_from=None):
+def _latent(heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, base, mlp, kv_from=None, rot_dims=None):
     m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": scale}
-    if rot_dim:
-        m["rot"] = {"base": base, "dims": rot_dim}
+    if rot_dim and base:
+        m["rot"] = {"base": base, "dims": rot_dim if rot_dims is None else rot_dims}
     if kv_from is not None:
         m["kv_from"] = kv_from
     return {"type": "latent_attention", "mixer": m, "mlp": mlp}
@@ -81,7 +81,7 @@ DODI_B = {
         _parallel(_left(1, 1, 8, 8, 0.35, 1), _right(1, 8, 8, 1.0, 1), {"kind": "dense", "ff": 24}),
         _latent(1, 6, 0, 6, 6, 6, 0.4, 0.0, _moe(2, 1, 12)),
         _parallel(_left(2, 2, 6, 10, 0.5, None, (10000.0, 6)), _right(2, 5, 7, 11.0, 3), _moe(3, 3, 8, (3, 3))),
-        _latent(2, 4, 6, 5, 7, 6, 0.5, 100.0, None),
+        _latent(2, 4, 6, 5, 7, 6, 0.5, 0.0, None),          # coordinates beside the head's that no rotation turns
     ],
 }
 DODI_B0 = {**{k: v for k, v in DODI_B.items() if k != "streams"}, "vocab": 67}      # plain residual sums
@@ -105,9 +105,9 @@ DODI_C = {
 DODI_D = {
     "architecture": "Dodilix", "vocab": 70, "width": 50, "streams": 5, "norm": {"eps": 1e-5}, "logit_scale": 0.8,
     "layers": [
-        _latent(2, 10, 8, 14, 12, 264, 0.2, 300.0, {"kind": "dense", "ff": 30}),
+        _latent(2, 10, 8, 14, 12, 264, 0.2, 300.0, {"kind": "dense", "ff": 30}, rot_dims=4),
         _parallel(_left(34, 2, 8, 6, 0.35, 21, (10.0, 4)), _right(1, 12, 20, 4.0, 2), None, (1.0, 0.5)),
-        _latent(3, 6, 8, 9, 10, 264, 0.25, 300.0, _moe(5, 2, 10, None, None, 0.7), kv_from=0),
+        _latent(3, 6, 8, 9, 10, 264, 0.25, 300.0, _moe(5, 2, 10, None, None, 0.7), kv_from=0, rot_dims=4),
     ],
 }
 

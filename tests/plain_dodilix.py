@@ -105,7 +105,8 @@ def latent_kv(h, w, pre, m, eps):
     r = m["kv_rank"]
     d = h @ w[pre + "dkv"].T
     c = rms_norm(d[:, :r], w[pre + "dkv.norm"], eps)
-    kr = rotate(d[:, None, r:], torch.arange(T), m.get("rot_dim", 0), (m.get("rot") or {}).get("base", 1.0), True)[:, 0]
+    rot = m.get("rot") or {}
+    kr = rotate(d[:, None, r:], torch.arange(T), rot.get("dims", m.get("rot_dim", 0)) if rot else 0, rot.get("base", 1.0), True)[:, 0]
     return c, kr
 
 
@@ -117,7 +118,8 @@ def latent_attention(h, w, pre, m, eps, kv):
     cq = rms_norm(h @ w[pre + "dq"].T, w[pre + "dq.norm"], eps)
     q = (cq @ w[pre + "uq"].T).view(T, H, d + dr)
     qn = q[..., :d]
-    qr = rotate(q[..., d:], torch.arange(T), dr, (m.get("rot") or {}).get("base", 1.0), True)
+    rot = m.get("rot") or {}
+    qr = rotate(q[..., d:], torch.arange(T), rot.get("dims", dr) if rot else 0, rot.get("base", 1.0), True)
     kn = (c @ w[pre + "uk"].T).view(T, H, d)
     v = (c @ w[pre + "uv"].T).view(T, H, dv)
     out = torch.zeros(T, H, dv, dtype=F64)

@@ -85,7 +85,7 @@ def _broken(path, value):
     (("layers", 2, "mixer", "kv_from"), 1, "kv_from"),
     (("layers", 2, "mixer", "kv_from"), 3, "kv_from"),
     (("layers", 2, "mixer", "kv_rank"), 32, "kv_from"),
-    (("layers", 0, "mixer", "rot", "dims"), 2, "rot_dim"),
+    (("layers", 0, "mixer", "rot", "dims"), 6, "rot.dims"),
     (("layers", 0, "mlp", "router", "top"), 5, "router"),
     (("layers", 0, "mlp", "kind"), "gated", "kind"),
     (("streams",), 40, "streams"),
