@@ -8,7 +8,8 @@
 //     O[16 heads x rank]   += P C        with the float32 weights P cut into three bfloat16 terms hi + mid + lo
 //                                        (p - hi - mid - lo is below 2^-24 p): each term's products are exact
 //                                        in the float32 accumulators, so the weighted sum is a float32 sum
-// The head's gate multiplies the result in the store.  Up to 16 heads (rows of the tile past the heads are zero),
+// The head's gate multiplies the result in the store.  Up to 16 heads (rows of the tile past the heads are zero; with
+// eight heads or fewer the tile's lower half takes the next query row),
 // rank a multiple of 32 fixed at compile time (-DNG_LAT_RANK).  Keys are walked in ascending order from the
 // window's first key: a row's result does not depend on the cut or the batch.
 #include "ng_common.cuh"
@@ -67,6 +68,10 @@ __device__ __forceinline__ void lm_split3(float x, float y, uint32_t& hi, uint32
     lo = lm_pack(xr - __bfloat162float(xm), yr - __bfloat162float(ym));
 }
 
+// PAIR (models of up to eight heads): the tile's lower eight rows are the heads of the NEXT query row, so no half of
+// a tile is empty.  Two rows share their key tiles when they are neighbours of one request (same entry, positions p and
+// p + 1); otherwise the warp takes them one after the other, each in the upper half.
+template <bool PAIR>
 __global__ void __launch_bounds__(LM_WARPS * 32)
 latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages, const int* __restrict__ table,
                        int table_stride, const int* __restrict__ positions, const int* __restrict__ row_entry,
@@ -76,26 +81,40 @@ latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ page
     ng_pdl_trigger();
     ng_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * LM_WARPS + warp;
-    if (row >= n_rows) return;
+    const int unit = blockIdx.x * LM_WARPS + warp;
+    const int first = PAIR ? 2 * unit : unit;
+    if (first >= n_rows) return;
     const int quad = lane >> 2, tq = lane & 3;             // heads quad and quad + 8; columns 2 tq, 2 tq + 1 of an 8-wide tile
+    bf16* bufs = reinterpret_cast<bf16*>(lm_smem) + (size_t)warp * 2 * LM_TILE * LM_LD;      // this warp's two tiles
+    bool together = false;
+    int n_pass = 1;
+    if (PAIR && first + 1 < n_rows) {
+        const int e0 = row_entry[first], e1 = row_entry[first + 1];
+        together = e0 >= 0 && e0 == e1 && positions[first + 1] == positions[first] + 1;
+        n_pass = together ? 1 : 2;
+    }
+    for (int pass = 0; pass < (PAIR ? n_pass : 1); ++pass) {
+    const int row = first + pass;                          // the row of the tile's upper half
+    const int row1 = together ? first + 1 : -1;            // PAIR: the row of its lower half, if it has one
     bf16* orow = out + (size_t)row * nH * LM_R;
     const int entry = row_entry[row];
     if (entry < 0) {
         for (int i = lane; i < nH * LM_R; i += 32) orow[i] = __float2bfloat16_rn(0.f);
-        return;
+        continue;
     }
     const int pos = positions[row];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int pos1 = row1 >= 0 ? pos + 1 : pos;            // the lower half's last and first visible key
+    const int lo1 = PAIR ? (window > 0 ? max(0, pos1 - window + 1) : 0) : lo;
+    const int pos_hi = pos1;                               // the last key any row of the tile sees
     const int* trow = table + (size_t)entry * table_stride;
-    bf16* bufs = reinterpret_cast<bf16*>(lm_smem) + (size_t)warp * 2 * LM_TILE * LM_LD;      // this warp's two tiles
 
-    // the row's queries as A fragments: heads quad and quad + 8, all of the latent's columns
+    // the queries as A fragments: rows quad (upper half) and quad + 8 (lower half), all of the latent's columns
     uint32_t qa[LM_R / 16][4];
     {
         const bf16* q0 = q + ((size_t)row * nH + quad) * LM_R;
-        const bf16* q1 = q0 + (size_t)8 * LM_R;
-        const bool h0 = quad < nH, h1 = quad + 8 < nH;
+        const bf16* q1 = PAIR ? q + ((size_t)max(row1, 0) * nH + quad) * LM_R : q0 + (size_t)8 * LM_R;
+        const bool h0 = quad < nH, h1 = PAIR ? (row1 >= 0 && quad < nH) : quad + 8 < nH;
 #pragma unroll
         for (int ks = 0; ks < LM_R / 16; ++ks) {
             const int d = ks * 16 + tq * 2;
@@ -111,9 +130,9 @@ latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ page
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
     constexpr int CPK = LM_R / 8;                              // 16-byte pieces of a key
-    // a tile is copied asynchronously while the one before it is used; keys past the row's last are zero
+    // a tile is copied asynchronously while the one before it is used; keys past the tile's last visible one are zero
     auto stage = [&](int k0, bf16* dst) {
-        const int n = min(LM_TILE, pos + 1 - k0);
+        const int n = min(LM_TILE, pos_hi + 1 - k0);
 #pragma unroll
         for (int i = 0; i < CPK; ++i) {
             const int c = lane + 32 * i;
@@ -132,12 +151,13 @@ latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ page
         }
         lm_cp_commit();
     };
+    __syncwarp();                                              // (a second pass: the tiles of the first are done with)
     stage(lo, bufs);
     int it = 0;
-    for (int k0 = lo; k0 <= pos; k0 += LM_TILE, ++it) {
-        const int n = min(LM_TILE, pos + 1 - k0);
+    for (int k0 = lo; k0 <= pos_hi; k0 += LM_TILE, ++it) {
+        const int n = min(LM_TILE, pos_hi + 1 - k0);
         const bf16* tile = bufs + (size_t)(it & 1) * LM_TILE * LM_LD;
-        if (k0 + LM_TILE <= pos) {
+        if (k0 + LM_TILE <= pos_hi) {
             stage(k0 + LM_TILE, bufs + (size_t)((it + 1) & 1) * LM_TILE * LM_LD);
             lm_cp_wait_but_one();
         } else {
@@ -157,15 +177,17 @@ latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ page
                 lm_mma(s[nt], qa[ks + 1], b[2], b[3]);
             }
         }
-        // online softmax of heads quad (values 0, 1 of a tile) and quad + 8 (values 2, 3)
+        // online softmax of the upper half's rows (values 0, 1 of a tile) and the lower half's (values 2, 3)
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const bool ok = nt * 8 + tq * 2 + e < n;
-                s[nt][e] = ok ? s[nt][e] * scale : -INFINITY;
-                s[nt][2 + e] = ok ? s[nt][2 + e] * scale : -INFINITY;
+                const int kidx = k0 + nt * 8 + tq * 2 + e;
+                const bool ok0 = PAIR ? kidx <= pos : nt * 8 + tq * 2 + e < n;
+                const bool ok1 = PAIR ? (row1 >= 0 && kidx >= lo1 && kidx <= pos1) : ok0;
+                s[nt][e] = ok0 ? s[nt][e] * scale : -INFINITY;
+                s[nt][2 + e] = ok1 ? s[nt][2 + e] * scale : -INFINITY;
                 mx0 = fmaxf(mx0, s[nt][e]);
                 mx1 = fmaxf(mx1, s[nt][2 + e]);
             }
@@ -174,8 +196,10 @@ latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ page
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);      // finite: key k0 is always visible
-        const float c0 = expf(m0 - mn0), c1 = expf(m1 - mn1);
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        // a half that has seen no key yet (a lower half without a row) keeps a running maximum of -inf: subtract 0 there
+        const float b0 = mn0, b1 = PAIR && mn1 == -INFINITY ? 0.f : mn1;     // (the upper half always sees the tile's first key)
+        const float c0 = expf(m0 - b0), c1 = expf(m1 - b1);
         m0 = mn0;
         m1 = mn1;
         float r0 = 0.f, r1 = 0.f;
@@ -183,8 +207,8 @@ latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ page
         for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                s[nt][e] = expf(s[nt][e] - mn0);
-                s[nt][2 + e] = expf(s[nt][2 + e] - mn1);
+                s[nt][e] = expf(s[nt][e] - b0);
+                s[nt][2 + e] = expf(s[nt][2 + e] - b1);
                 r0 += s[nt][e];
                 r1 += s[nt][2 + e];
             }
@@ -233,14 +257,19 @@ latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ page
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const int h0 = quad, h1 = quad + 8;
-    const float f0 = h0 < nH ? (l0 > 0.f ? 1.f / l0 : 0.f) * (gate ? gate[(size_t)row * nH + h0] : 1.f) : 0.f;
-    const float f1 = h1 < nH ? (l1 > 0.f ? 1.f / l1 : 0.f) * (gate ? gate[(size_t)row * nH + h1] : 1.f) : 0.f;
+    // where the two halves' results go: (row, head quad) and, lower half, (row, head quad + 8) or (the next row, head quad)
+    const int h0 = quad, h1 = PAIR ? quad : quad + 8;
+    const int out_row1 = PAIR ? row1 : row;
+    const bool st0 = h0 < nH, st1 = out_row1 >= 0 && h1 < nH;
+    const float f0 = st0 ? (l0 > 0.f ? 1.f / l0 : 0.f) * (gate ? gate[(size_t)row * nH + h0] : 1.f) : 0.f;
+    const float f1 = st1 ? (l1 > 0.f ? 1.f / l1 : 0.f) * (gate ? gate[(size_t)out_row1 * nH + h1] : 1.f) : 0.f;
+    bf16* orow1 = out + (size_t)max(out_row1, 0) * nH * LM_R;
 #pragma unroll
     for (int t = 0; t < LM_R / 8; ++t) {
         const int d = t * 8 + tq * 2;
-        if (h0 < nH) *reinterpret_cast<uint32_t*>(orow + (size_t)h0 * LM_R + d) = lm_pack(o[t][0] * f0, o[t][1] * f0);
-        if (h1 < nH) *reinterpret_cast<uint32_t*>(orow + (size_t)h1 * LM_R + d) = lm_pack(o[t][2] * f1, o[t][3] * f1);
+        if (st0) *reinterpret_cast<uint32_t*>(orow + (size_t)h0 * LM_R + d) = lm_pack(o[t][0] * f0, o[t][1] * f0);
+        if (st1) *reinterpret_cast<uint32_t*>(orow1 + (size_t)h1 * LM_R + d) = lm_pack(o[t][2] * f1, o[t][3] * f1);
+    }
     }
 }
 
@@ -253,12 +282,20 @@ NG_EXPORT int ng_latent_core_mma(const void* q, const void* pages, const int* ta
     const size_t smem = (size_t)LM_WARPS * 2 * LM_TILE * LM_LD * sizeof(bf16);
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(latent_core_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(latent_core_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+            cudaFuncSetAttribute(latent_core_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return NG_LAUNCH_FAILED;
         configured = true;
     }
-    NG_LAUNCH((latent_core_mma_kernel), (n_rows + LM_WARPS - 1) / LM_WARPS, LM_WARPS * 32, smem, stream, (const bf16*)q,
-              (const bf16*)pages, table, table_stride, positions, row_entry, gate, (bf16*)out, n_rows, nH, page_size, num_pages,
-              window, scale);
+    if (nH <= 8) {                  // two query rows a tile
+        const int units = (n_rows + 1) / 2;
+        NG_LAUNCH((latent_core_mma_kernel<true>), (units + LM_WARPS - 1) / LM_WARPS, LM_WARPS * 32, smem, stream, (const bf16*)q,
+                  (const bf16*)pages, table, table_stride, positions, row_entry, gate, (bf16*)out, n_rows, nH, page_size,
+                  num_pages, window, scale);
+    } else {
+        NG_LAUNCH((latent_core_mma_kernel<false>), (n_rows + LM_WARPS - 1) / LM_WARPS, LM_WARPS * 32, smem, stream, (const bf16*)q,
+                  (const bf16*)pages, table, table_stride, positions, row_entry, gate, (bf16*)out, n_rows, nH, page_size,
+                  num_pages, window, scale);
+    }
     return ng_launch_status();
 }
