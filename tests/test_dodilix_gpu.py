@@ -348,6 +348,32 @@ def test_heads_expanded_and_gated(dtype, n, H, rp, rank, dv):
     assert rel_err(wide[:, 4:4 + H * dv], want) < TOL[dtype] and float(wide[:, :4].abs().max()) == 0
 
 
+@pytest.mark.parametrize("H,rp", [(8, 64), (3, 32), (5, 128), (16, 64)])
+@pytest.mark.parametrize("window", [None, 37, 1])
+def test_latent_core_on_tensor_cores_with_two_rows_a_tile(H, rp, window):
+    """Models of up to eight heads put two neighbouring query rows into one tile; rows that are no neighbours (another
+    request, a padding row, an odd row at the end) run one after the other.  A ragged step against the plain statement."""
+    dtype = torch.bfloat16
+    lens, before = [1, 5, 1, 2, 70, 3, 1], [40, 0, 99, 7, 30, 200, 0]
+    re, pos = [], []
+    for e, (n, b) in enumerate(zip(lens, before)):
+        re += [e] * n
+        pos += list(range(b, b + n))
+    re, pos = re + [-1, -1, len(lens) - 1], pos + [0, 0, 1]          # padding rows, then the last request's next token
+    n, ps = len(re), 16
+    g = torch.Generator().manual_seed(H)
+    pages = _x((64, 1, ps, rp), dtype, seed=3)
+    table = torch.stack([torch.randperm(64, generator=g)[:16] for _ in lens]).to(torch.int32).to(DEV)
+    q = _x((n, H * rp), dtype, seed=5, scale=0.3)
+    gate = torch.rand(n, H, generator=g).to(DEV)
+    out = torch.full((n, H * rp), 7.0, dtype=dtype, device=DEV)
+    want = torch.zeros(n, H * rp, dtype=F64)
+    ops().latent_core_mma(q, pages, table, _i32(pos), _i32(re), gate, out, H, window, 0.11)
+    refs.latent_core(q.cpu(), pages.cpu(), table.cpu(), torch.tensor(pos), torch.tensor(re), gate.cpu(), want, H, window, 0.11)
+    assert rel_err(out, want) < TOL[dtype]
+    assert float(out[-3:-1].abs().max()) == 0                        # rows of no entry get zeros
+
+
 # ------------------------------------------------------------------------------------------ routed experts
 @pytest.mark.parametrize("E,top,groups,keep,scale", [(8, 3, 4, 2, 2.25), (6, 2, 3, 1, 1.7), (4, 1, 1, 1, 1.0), (16, 4, 4, 2, 0.5),
                                                      (3, 3, 3, 3, 1.0)])
